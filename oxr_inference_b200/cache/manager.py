@@ -59,7 +59,8 @@ class CacheManager:
         self.plan, self.page_size, self.num_pages, self.max_requests = plan, page_size, num_pages, max_requests
         self.pools = [PagePool(num_pages) for _ in plan.groups]
         self.windows = [g.need.window for g in plan.groups]
-        self._windowed = [g for g, w in enumerate(self.windows) if w > 0]
+        self.chunks = [g.need.chunk for g in plan.groups]
+        self._windowed = [g for g in range(len(plan.groups)) if self.windows[g] > 0 or self.chunks[g] > 0]
         self._free_slots = list(range(max_requests - 1, -1, -1))
         self._open: dict[int, RequestCache] = {}
         self.scratch_slot = max_requests
@@ -80,23 +81,26 @@ class CacheManager:
         self.states: list[torch.Tensor] = []
         if device is not None:
             for g in plan.groups:
-                shape = (g.num_layers, num_pages, page_size, g.need.num_kv_heads, g.need.head_dim)
-                self.k_pools.append(torch.zeros(shape, dtype=dtype, device=device))
-                self.v_pools.append(torch.zeros(shape, dtype=dtype, device=device))
+                shape = (g.num_layers, num_pages, page_size, g.need.num_kv_heads)
+                self.k_pools.append(torch.zeros((*shape, g.need.head_dim), dtype=dtype, device=device))
+                # a group whose values are read from its key rows has no value pool
+                self.v_pools.append(torch.zeros((*shape, g.need.v_dim), dtype=dtype, device=device) if g.need.v_dim > 0 else None)
             for s in plan.states:
                 self.states.append(torch.zeros((max_requests + 1, *s.shape), dtype=s.dtype, device=device))
         self.kv_maps: list = [None] * len(self.k_pools)
         if device is not None and torch.device(device).type == "cuda":
             from oxr_inference_b200 import ops
 
-            self.kv_maps = [ops.make_kv_maps(k, v, page_size) for k, v in zip(self.k_pools, self.v_pools)]
+            # TMA maps serve the kernels of plain grouped-query attention: keys and values of one size, causal or windowed
+            self.kv_maps = [ops.make_kv_maps(k, v, page_size) if (g.need.value_dim is None and g.need.chunk == 0) else None
+                            for g, k, v in zip(plan.groups, self.k_pools, self.v_pools)]
 
     # ---- sizes
     @staticmethod
     def bytes_per_page(plan: CachePlan, page_size: int, dtype: torch.dtype) -> int:
         """Bytes of one page id over all groups and layers (oxr_runtime/kv_cache.py:34-37)."""
         element = torch.empty((), dtype=dtype).element_size()
-        return sum(2 * g.num_layers * page_size * g.need.num_kv_heads * g.need.head_dim * element for g in plan.groups)
+        return sum(g.num_layers * page_size * g.need.num_kv_heads * (g.need.head_dim + g.need.v_dim) * element for g in plan.groups)
 
     @property
     def free_pages(self) -> int:
@@ -125,8 +129,11 @@ class CacheManager:
 
     def _first_needed_page(self, group: int, start: int) -> int:
         """Index of the first page that a query at position ``start`` or later can still see."""
-        w = self.windows[group]
-        return 0 if w <= 0 else max(0, start - w + 1) // self.page_size
+        w, c = self.windows[group], self.chunks[group]
+        first = 0 if w <= 0 else max(0, start - w + 1)
+        if c > 0:
+            first = max(first, start // c * c)   # nothing before the query's own chunk is ever seen again
+        return first // self.page_size
 
     def reserve(self, rc: RequestCache, new_length: int) -> bool:
         """Make room for the tokens at positions [rc.length, new_length). False, with nothing taken, if any

@@ -17,8 +17,14 @@ class Architecture:
     name: str
     config_from_dict: Callable[[Mapping[str, Any], Mapping[str, Any] | None], Any]
     """(config.json, generation_config.json or None) -> typed config."""
-    model_spec: Callable[[Any], Any]
+    model_spec: Callable[..., Any]
     """typed config -> :class:`oxr_inference_b200.parts.spec.ModelSpec`."""
+    shapes_matter: bool = False
+    """The design leaves some sizes to the shapes of its tensors: ``model_spec`` then takes a second argument, checkpoint name ->
+    shape (or None, when there is no checkpoint, as in random-weights mode)."""
+
+    def spec_for(self, config: Any, tensor_shapes: Mapping[str, tuple[int, ...]] | None = None) -> Any:
+        return self.model_spec(config, tensor_shapes) if self.shapes_matter else self.model_spec(config)
 
 
 ARCHITECTURES: dict[str, Architecture] = {}
@@ -41,6 +47,8 @@ def resolve_architecture(raw_config: Mapping[str, Any]) -> Architecture:
 
     _load_builtin()
     names = raw_config.get("architectures")
+    if not names and isinstance(raw_config.get("architecture"), str):
+        names = [raw_config["architecture"]]   # some designs name themselves with one string
     if not names:
         raise ConfigError(f"config.json has no 'architectures' entry; known: {sorted(ARCHITECTURES)}")
     name = names[0]

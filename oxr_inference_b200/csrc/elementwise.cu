@@ -10,7 +10,7 @@ OXR_TL_DEFINE(oxr_tl_read_elem)
 // ---------------------------------------------------------------------------------------------- embedding
 template <typename TT, typename TO>
 __global__ void embedding_kernel(TO* __restrict__ out, const TT* __restrict__ table, const int* __restrict__ ids,
-                                 int hidden, int vocab, int* status) {
+                                 int hidden, int vocab, float scale, int* status) {
     const int t = blockIdx.x;
     const int id = ids[t];
     TO* dst = out + (size_t)t * hidden;
@@ -20,7 +20,7 @@ __global__ void embedding_kernel(TO* __restrict__ out, const TT* __restrict__ ta
         return;
     }
     const TT* src = table + (size_t)id * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = Num<TO>::from_f32(Num<TT>::to_f32(src[i]));
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = Num<TO>::from_f32(Num<TT>::to_f32(src[i]) * scale);
 }
 
 // 16-byte copies when table and output share a dtype and a row is a whole number of 16-byte words.
@@ -39,12 +39,12 @@ __global__ void embedding_vec_kernel(T* __restrict__ out, const T* __restrict__ 
     for (int i = threadIdx.x; i < words_per_row; i += blockDim.x) dst[i] = __ldg(src + i);
 }
 
-// table_dtype / out_dtype: 0 = float32, 1 = bfloat16
+// table_dtype / out_dtype: 0 = float32, 1 = bfloat16. out = table[id] * scale, the product in fp32, rounded once.
 OXR_API int oxr_embedding(void* out, const void* table, const int* ids, int n_tokens, int hidden, int vocab,
-                          int table_dtype, int out_dtype, int* status, cudaStream_t stream) {
+                          int table_dtype, int out_dtype, float scale, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const int threads = 256;
-    if (table_dtype == out_dtype) {
+    if (table_dtype == out_dtype && scale == 1.f) {
         const int esize = table_dtype == 0 ? 4 : 2;
         const bool aligned = ((size_t)hidden * esize) % 16 == 0 && ((uintptr_t)out % 16 == 0) && ((uintptr_t)table % 16 == 0);
         if (aligned) {
@@ -57,13 +57,13 @@ OXR_API int oxr_embedding(void* out, const void* table, const int* ids, int n_to
         }
     }
     if (table_dtype == 0 && out_dtype == 0)
-        embedding_kernel<float, float><<<n_tokens, threads, 0, stream>>>((float*)out, (const float*)table, ids, hidden, vocab, status);
+        embedding_kernel<float, float><<<n_tokens, threads, 0, stream>>>((float*)out, (const float*)table, ids, hidden, vocab, scale, status);
     else if (table_dtype == 1 && out_dtype == 1)
-        embedding_kernel<__nv_bfloat16, __nv_bfloat16><<<n_tokens, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)table, ids, hidden, vocab, status);
+        embedding_kernel<__nv_bfloat16, __nv_bfloat16><<<n_tokens, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)table, ids, hidden, vocab, scale, status);
     else if (table_dtype == 0 && out_dtype == 1)
-        embedding_kernel<float, __nv_bfloat16><<<n_tokens, threads, 0, stream>>>((__nv_bfloat16*)out, (const float*)table, ids, hidden, vocab, status);
+        embedding_kernel<float, __nv_bfloat16><<<n_tokens, threads, 0, stream>>>((__nv_bfloat16*)out, (const float*)table, ids, hidden, vocab, scale, status);
     else if (table_dtype == 1 && out_dtype == 0)
-        embedding_kernel<__nv_bfloat16, float><<<n_tokens, threads, 0, stream>>>((float*)out, (const __nv_bfloat16*)table, ids, hidden, vocab, status);
+        embedding_kernel<__nv_bfloat16, float><<<n_tokens, threads, 0, stream>>>((float*)out, (const __nv_bfloat16*)table, ids, hidden, vocab, scale, status);
     else
         return OXR_BAD_ARGUMENT;
     return oxr_launch_status();

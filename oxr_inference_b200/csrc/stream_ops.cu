@@ -1,0 +1,169 @@
+// Operations on a residual stream that is kept whole in fp32: RMSNorm of the stream, the post-norm add
+// (stream += norm(y) * w, optionally followed by the next pre-norm in the same pass), the concatenation that feeds a
+// re-entry map, a broadcast row add, a gated feed-forward activation with clamps, and per-step rotary angles.
+//
+// All arithmetic is fp32 (the angles: fp64, rounded once); T is the activation type that the products read and write.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------------- norm of the stream
+// One block per output row; row r reads stream row `rows ? rows[r] : r`. out = x * rsqrt(mean(x^2) + eps) * weight.
+template <typename T>
+__global__ void stream_rms_norm_kernel(T* __restrict__ out, const float* __restrict__ stream, const float* __restrict__ weight,
+                                       const int* __restrict__ rows, int hidden, float eps) {
+    __shared__ float red[32];
+    const int r = blockIdx.x;
+    const float* x = stream + (size_t)(rows ? rows[r] : r) * hidden;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) ss = fmaf(x[i], x[i], ss);
+    ss = block_sum(ss, red);
+    const float inv = 1.f / sqrtf(ss / (float)hidden + eps);
+    T* dst = out + (size_t)r * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = Num<T>::from_f32(x[i] * inv * weight[i]);
+}
+
+// stream[r] += y[r] * rsqrt(mean(y[r]^2) + eps) * w_post; then, when `out` is given, out[r] = norm(stream[r]) * w_next.
+// One block per row; the updated row is kept in shared memory for the second norm when it fits.
+template <typename T>
+__global__ void norm_add_norm_kernel(float* __restrict__ stream, const T* __restrict__ y, const float* __restrict__ w_post,
+                                     T* __restrict__ out, const float* __restrict__ w_next, int hidden, float eps_post, float eps_next,
+                                     int row_floats_in_smem) {
+    extern __shared__ float smem[];
+    float* red = smem;
+    float* rowbuf = smem + 32;
+    const size_t at = (size_t)blockIdx.x * hidden;
+    const bool cached = row_floats_in_smem >= hidden;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = Num<T>::to_f32(y[at + i]);
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.f / sqrtf(ss / (float)hidden + eps_post);
+    float s2 = 0.f;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = stream[at + i] + Num<T>::to_f32(y[at + i]) * inv * w_post[i];
+        stream[at + i] = v;
+        if (cached) rowbuf[i] = v;
+        s2 = fmaf(v, v, s2);
+    }
+    if (out == nullptr) return;
+    s2 = block_sum(s2, red);
+    const float inv2 = 1.f / sqrtf(s2 / (float)hidden + eps_next);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float v = cached ? rowbuf[i] : stream[at + i];   // written by this same thread above
+        out[at + i] = Num<T>::from_f32(v * inv2 * w_next[i]);
+    }
+}
+
+// out[r] = [ a[r] | b[r] ] rounded to T
+template <typename T>
+__global__ void concat2_cast_kernel(T* __restrict__ out, const float* __restrict__ a, const float* __restrict__ b, int hidden, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t r = i / (2 * hidden);
+        const int c = (int)(i % (2 * hidden));
+        out[i] = Num<T>::from_f32(c < hidden ? a[r * hidden + c] : b[r * hidden + (c - hidden)]);
+    }
+}
+
+__global__ void add_row_f32_kernel(float* __restrict__ x, const float* __restrict__ row, int hidden, size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) x[i] += row[i % hidden];
+}
+
+// ---------------------------------------------------------------------------------------------- clamped gated unit
+// out = g' * sigmoid(alpha * g') * (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit); gate_up rows are
+// [gate | up] (interleave 0) or gate and up alternating in groups of `interleave` columns.
+template <typename T>
+__global__ void clamped_glu_kernel(T* __restrict__ out, const T* __restrict__ gate_up, int inter, int interleave, float alpha, float limit,
+                                   size_t total) {
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        const size_t row = i / inter;
+        const int col = (int)(i % inter);
+        size_t gi, ui;
+        if (interleave) {
+            gi = row * 2 * inter + (size_t)(col / interleave) * 2 * interleave + col % interleave;
+            ui = gi + interleave;
+        } else {
+            gi = row * 2 * inter + col;
+            ui = gi + inter;
+        }
+        const float g = fminf(Num<T>::to_f32(gate_up[gi]), limit);
+        const float u = fminf(fmaxf(Num<T>::to_f32(gate_up[ui]), -limit), limit);
+        out[i] = Num<T>::from_f32(g / (1.f + expf(-alpha * g)) * (u + 1.f));
+    }
+}
+
+// ---------------------------------------------------------------------------------------------- rotary angles
+// cos/sin [tokens, half] of position * freq[i], the product and the functions in fp64, rounded once to fp32.
+__global__ void rotary_angles_kernel(float* __restrict__ cos_out, float* __restrict__ sin_out, const int* __restrict__ positions,
+                                     const double* __restrict__ freq, int half, int total) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    double s, c;
+    sincos((double)positions[i / half] * freq[i % half], &s, &c);
+    cos_out[i] = (float)c;
+    sin_out[i] = (float)s;
+}
+
+// ---------------------------------------------------------------------------------------------- launchers
+static inline int grid_for(size_t total, int threads) {
+    size_t b = (total + threads - 1) / threads;
+    return (int)(b < 1 ? 1 : (b > 148 * 16 ? 148 * 16 : b));
+}
+
+OXR_API int oxr_stream_rms_norm(void* out, const float* stream, const float* weight, const int* rows, int n_out, int hidden, float eps,
+                                int dtype, cudaStream_t stream_) {
+    if (n_out <= 0) return 0;
+    if (hidden <= 0) return OXR_BAD_ARGUMENT;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (dtype == 0) stream_rms_norm_kernel<float><<<n_out, threads, 0, stream_>>>((float*)out, stream, weight, rows, hidden, eps);
+    else stream_rms_norm_kernel<__nv_bfloat16><<<n_out, threads, 0, stream_>>>((__nv_bfloat16*)out, stream, weight, rows, hidden, eps);
+    return oxr_launch_status();
+}
+
+OXR_API int oxr_norm_add_norm(float* stream, const void* y, const float* w_post, void* out, const float* w_next, int n, int hidden,
+                              float eps_post, float eps_next, int dtype, cudaStream_t stream_) {
+    if (n <= 0) return 0;
+    if (hidden <= 0 || (out != nullptr && w_next == nullptr)) return OXR_BAD_ARGUMENT;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    const int keep = hidden <= 8192 ? hidden : 0;
+    const size_t smem = (32 + keep) * sizeof(float);
+    if (dtype == 0)
+        norm_add_norm_kernel<float><<<n, threads, smem, stream_>>>(stream, (const float*)y, w_post, (float*)out, w_next, hidden, eps_post, eps_next, keep);
+    else
+        norm_add_norm_kernel<__nv_bfloat16><<<n, threads, smem, stream_>>>(stream, (const __nv_bfloat16*)y, w_post, (__nv_bfloat16*)out, w_next, hidden,
+                                                                          eps_post, eps_next, keep);
+    return oxr_launch_status();
+}
+
+OXR_API int oxr_concat2_cast(void* out, const float* a, const float* b, int n, int hidden, int dtype, cudaStream_t stream_) {
+    if (n <= 0) return 0;
+    const size_t total = (size_t)n * 2 * hidden;
+    if (dtype == 0) concat2_cast_kernel<float><<<grid_for(total, 256), 256, 0, stream_>>>((float*)out, a, b, hidden, total);
+    else concat2_cast_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, stream_>>>((__nv_bfloat16*)out, a, b, hidden, total);
+    return oxr_launch_status();
+}
+
+OXR_API int oxr_add_row_f32(float* x, const float* row, int n, int hidden, cudaStream_t stream_) {
+    if (n <= 0) return 0;
+    const size_t total = (size_t)n * hidden;
+    add_row_f32_kernel<<<grid_for(total, 256), 256, 0, stream_>>>(x, row, hidden, total);
+    return oxr_launch_status();
+}
+
+OXR_API int oxr_clamped_glu(void* out, const void* gate_up, int n, int inter, int interleave, float alpha, float limit, int dtype,
+                            cudaStream_t stream_) {
+    if (n <= 0) return 0;
+    if (inter <= 0 || interleave < 0 || (interleave && inter % interleave)) return OXR_BAD_ARGUMENT;
+    const size_t total = (size_t)n * inter;
+    if (dtype == 0) clamped_glu_kernel<float><<<grid_for(total, 256), 256, 0, stream_>>>((float*)out, (const float*)gate_up, inter, interleave, alpha, limit, total);
+    else clamped_glu_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, stream_>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, inter, interleave,
+                                                                                     alpha, limit, total);
+    return oxr_launch_status();
+}
+
+OXR_API int oxr_rotary_angles(float* cos_out, float* sin_out, const int* positions, const double* freq, int n, int half, cudaStream_t stream_) {
+    if (n <= 0 || half <= 0) return 0;
+    const int total = n * half;
+    rotary_angles_kernel<<<(total + 127) / 128, 128, 0, stream_>>>(cos_out, sin_out, positions, freq, half, total);
+    return oxr_launch_status();
+}

@@ -26,7 +26,8 @@ from oxr_inference_b200.engine.graphs import DecodeGraphs
 from oxr_inference_b200.engine.runtime import DTYPES, ModelRunner
 from oxr_inference_b200.engine.scheduler import Busy, Request, Scheduler, StepPlan  # noqa: F401
 from oxr_inference_b200.sampling.params import Completion, SamplingParams  # noqa: F401
-from oxr_inference_b200.weights.loader import load_weights
+from oxr_inference_b200.config.registry import resolve_architecture
+from oxr_inference_b200.weights.loader import load_weights, tensor_shapes
 from oxr_inference_b200.weights.random_init import fill_random
 
 log = logging.getLogger(__name__)
@@ -68,8 +69,9 @@ class Engine:
             raw, generation = read_config_json(model_dir)
         else:
             raw, generation = dict(random_config), None
+        shapes = tensor_shapes(model_dir) if model_dir is not None and resolve_architecture(raw).shapes_matter else None
         model, self.config = ModelRunner.build_model(raw, generation, dtype=s.dtype, device=device, max_positions=s.max_positions,
-                                                      page_size=s.page_size)
+                                                      page_size=s.page_size, shapes=shapes)
         if model_dir is not None:
             load_weights(model, model_dir)
         else:

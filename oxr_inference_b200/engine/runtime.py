@@ -14,7 +14,7 @@ from oxr_inference_b200.config.registry import resolve_architecture
 from oxr_inference_b200.engine.batch import BatchBuilder, StepEntry
 from oxr_inference_b200.parts.base import Runtime
 from oxr_inference_b200.parts.decoder import DecoderModel
-from oxr_inference_b200.weights.loader import load_weights
+from oxr_inference_b200.weights.loader import load_weights, tensor_shapes
 from oxr_inference_b200.weights.random_init import fill_random
 
 DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32, "bf16": torch.bfloat16, "fp32": torch.float32}
@@ -50,11 +50,13 @@ class ModelRunner:
     # ---- construction
     @staticmethod
     def build_model(raw_config: Mapping[str, Any], generation: Mapping[str, Any] | None, *, dtype: str,
-                    device: str | torch.device = "cuda", max_positions: int | None = None, page_size: int = 16):
+                    device: str | torch.device = "cuda", max_positions: int | None = None, page_size: int = 16,
+                    shapes: Mapping[str, tuple[int, ...]] | None = None):
+        """``shapes``: the checkpoint's tensor shapes, for designs that leave a size to them (``Architecture.shapes_matter``)."""
         dev = require_cuda(device)
         arch = resolve_architecture(raw_config)
         config = arch.config_from_dict(raw_config, generation)
-        spec = arch.model_spec(config)
+        spec = arch.spec_for(config, shapes)
         runtime = Runtime(device=dev, dtype=DTYPES[dtype], max_positions=max_positions or spec.max_positions,
                           status=ops.new_status(dev), page_size=page_size)
         return DecoderModel(spec, runtime), config
@@ -63,7 +65,9 @@ class ModelRunner:
     def from_folder(cls, model_dir: str | Path, *, dtype: str, page_size: int, num_pages: int, max_requests: int,
                     device: str | torch.device = "cuda", max_positions: int | None = None) -> "ModelRunner":
         raw, generation = read_config_json(model_dir)
-        model, config = cls.build_model(raw, generation, dtype=dtype, device=device, max_positions=max_positions, page_size=page_size)
+        arch = resolve_architecture(raw)
+        model, config = cls.build_model(raw, generation, dtype=dtype, device=device, max_positions=max_positions, page_size=page_size,
+                                        shapes=tensor_shapes(model_dir) if arch.shapes_matter else None)
         load_weights(model, model_dir)
         return cls(model, config, page_size=page_size, num_pages=num_pages, max_requests=max_requests)
 

@@ -97,7 +97,7 @@ def _lib():
     if _core is None:
         lib = build.core_library()
         p, i, f = c_void_p, c_int, c_float
-        lib.oxr_embedding.argtypes = [p, p, p, i, i, i, i, i, p, p]
+        lib.oxr_embedding.argtypes = [p, p, p, i, i, i, i, i, f, p, p]
         lib.oxr_add_rms_norm.argtypes = [p, p, p, p, p, p, i, i, f, i, p]
         lib.oxr_silu_mul.argtypes = [p, p, i, i, i, i, p]
         lib.oxr_cast.argtypes = [p, p, c_size_t, i, i, p]
@@ -124,6 +124,24 @@ def _lib():
         lib.oxr_sample_chunks.restype = c_int
         lib.oxr_repetition_penalty.argtypes = [p, p, p, p, i, i, p]
         lib.oxr_mark_seen.argtypes = [p, p, p, i, i, p]
+        ll = c_longlong
+        lib.oxr_stream_rms_norm.argtypes = [p, p, p, p, i, i, f, i, p]
+        lib.oxr_norm_add_norm.argtypes = [p, p, p, p, p, i, i, f, f, i, p]
+        lib.oxr_concat2_cast.argtypes = [p, p, p, i, i, i, p]
+        lib.oxr_add_row_f32.argtypes = [p, p, i, i, p]
+        lib.oxr_clamped_glu.argtypes = [p, p, i, i, i, f, f, i, p]
+        lib.oxr_rotary_angles.argtypes = [p, p, p, p, i, i, p]
+        lib.oxr_mamba_conv.argtypes = [p, p, i, i, i, i, i, i, p, p, p, ll, p, p, p, i, p]
+        lib.oxr_mamba_scan.argtypes = [p, p, p, i, i, i, i, i, i, i, p, p, p, p, ll, p, p, i, p]
+        lib.oxr_gated_group_norm.argtypes = [p, p, p, i, i, i, p, i, i, f, i, p]
+        lib.oxr_attention_rows.argtypes = [p, p, i, p, ll, i, p, ll, i, i, i, i, i, i, p, p, p, i, i, i, f, i, i, p, i, p, i, p, p]
+        lib.oxr_scatter_rows.argtypes = [p, ll, ll, p, i, i, i, p, i, i, p, p]
+        lib.oxr_latent_prep.argtypes = [p, ll, ll, p, i, i, p, f, p, i, i, i, p, i, i, p, p, i, p, i, i, p, p]
+        lib.oxr_head_linear.argtypes = [p, i, i, p, i, i, p, i, i, i, i, i, p]
+        for name in ("oxr_stream_rms_norm", "oxr_norm_add_norm", "oxr_concat2_cast", "oxr_add_row_f32", "oxr_clamped_glu", "oxr_rotary_angles",
+                     "oxr_mamba_conv", "oxr_mamba_scan", "oxr_gated_group_norm", "oxr_attention_rows", "oxr_scatter_rows", "oxr_latent_prep",
+                     "oxr_head_linear"):
+            getattr(lib, name).restype = c_int
         for name in ("oxr_embedding", "oxr_add_rms_norm", "oxr_silu_mul", "oxr_cast", "oxr_qk_norm_rope_store",
                      "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_gemm_skinny_gated_bf16", "oxr_gemm_stream_bf16", "oxr_gemm_stream_gated_bf16", "oxr_gemm_tcgen05_bf16", "oxr_gemm_tcgen05_pair_bf16", "oxr_gemm_tcgen05_gated_bf16", "oxr_gemm_few_rows_cluster_bf16", "oxr_gemm_few_rows_max_clusters",
                      "oxr_gemm_tcgen05_pair_gated_bf16", "oxr_sample", "oxr_repetition_penalty", "oxr_mark_seen"):
@@ -212,14 +230,14 @@ def check_status(status: torch.Tensor) -> None:
 
 
 # --------------------------------------------------------------------------------------------------- ops
-def embedding(ids: torch.Tensor, table: torch.Tensor, out_dtype: torch.dtype, status: torch.Tensor) -> torch.Tensor:
-    """``out[t] = table[ids[t]]`` (oxr_runtime/decode_graph.py:75); an id outside the table sets the status word."""
+def embedding(ids: torch.Tensor, table: torch.Tensor, out_dtype: torch.dtype, status: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """``out[t] = table[ids[t]] * scale`` (oxr_runtime/decode_graph.py:75 has no scale); an id outside the table sets the status word."""
     _need(ids, "ids", torch.int32)
     _need(table, "table")
     n, (vocab, hidden) = ids.numel(), table.shape
     out = torch.empty((n, hidden), dtype=out_dtype, device=table.device)
     code = _lib().oxr_embedding(out.data_ptr(), table.data_ptr(), ids.data_ptr(), n, hidden, vocab, _dtype_code(table),
-                                _DT[out_dtype], status.data_ptr(), _stream())
+                                _DT[out_dtype], float(scale), status.data_ptr(), _stream())
     _done(code, "embedding")
     return out
 
@@ -937,3 +955,222 @@ def mark_seen(seen: torch.Tensor, slots: torch.Tensor, tokens: torch.Tensor) -> 
     _need(tokens, "tokens", torch.int32)
     code = _lib().oxr_mark_seen(seen.data_ptr(), slots.data_ptr(), tokens.data_ptr(), tokens.numel(), seen.shape[1], _stream())
     _done(code, "mark_seen")
+
+
+# --------------------------------------------------------------------------------------------------- a whole fp32 stream
+def stream_rms_norm(stream: torch.Tensor, weight: torch.Tensor, eps: float, out_dtype: torch.dtype, rows: torch.Tensor | None = None) -> torch.Tensor:
+    """``stream * rsqrt(mean(stream^2) + eps) * weight`` of an fp32 stream ``[tokens, hidden]``, rounded to ``out_dtype``; with
+    ``rows`` (int32) only those rows, output row i from stream row ``rows[i]``."""
+    _need(stream, "stream", torch.float32)
+    _need(weight, "weight", torch.float32)
+    n, hidden = stream.shape
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        n = rows.numel()
+    out = torch.empty((n, hidden), dtype=out_dtype, device=stream.device)
+    _done(_lib().oxr_stream_rms_norm(out.data_ptr(), stream.data_ptr(), weight.data_ptr(), _ptr(rows), n, hidden, float(eps), _DT[out_dtype], _stream()),
+          "stream_rms_norm")
+    return out
+
+
+def norm_add_norm(stream: torch.Tensor, y: torch.Tensor, post_weight: torch.Tensor, post_eps: float, next_weight: torch.Tensor | None = None,
+                  next_eps: float = 0.0) -> torch.Tensor | None:
+    """In place ``stream += rmsnorm(y) * post_weight`` (fp32); with ``next_weight`` also returns ``rmsnorm(stream) * next_weight`` in
+    ``y.dtype``: a sublayer's post-norm, the residual add and the next sublayer's pre-norm in one pass over the row."""
+    _need(stream, "stream", torch.float32)
+    _need(y, "y")
+    _need(post_weight, "post_weight", torch.float32)
+    if y.shape != stream.shape:
+        raise KernelError(f"norm_add_norm: y {tuple(y.shape)} does not match the stream {tuple(stream.shape)}")
+    n, hidden = stream.shape
+    out = None
+    if next_weight is not None:
+        _need(next_weight, "next_weight", torch.float32)
+        out = torch.empty((n, hidden), dtype=y.dtype, device=y.device)
+    _done(_lib().oxr_norm_add_norm(stream.data_ptr(), y.data_ptr(), post_weight.data_ptr(), _ptr(out), _ptr(next_weight), n, hidden, float(post_eps),
+                                   float(next_eps), _dtype_code(y), _stream()), "norm_add_norm")
+    return out
+
+
+def concat2_cast(a: torch.Tensor, b: torch.Tensor, out_dtype: torch.dtype) -> torch.Tensor:
+    """``[a | b]`` along the last axis for two fp32 ``[tokens, hidden]`` tensors, rounded to ``out_dtype``."""
+    _need(a, "a", torch.float32)
+    _need(b, "b", torch.float32)
+    if a.shape != b.shape:
+        raise KernelError("concat2_cast: shapes differ")
+    n, hidden = a.shape
+    out = torch.empty((n, 2 * hidden), dtype=out_dtype, device=a.device)
+    _done(_lib().oxr_concat2_cast(out.data_ptr(), a.data_ptr(), b.data_ptr(), n, hidden, _DT[out_dtype], _stream()), "concat2_cast")
+    return out
+
+
+def add_row_(x: torch.Tensor, row: torch.Tensor) -> torch.Tensor:
+    """In place ``x[t] += row`` for fp32 ``x [tokens, hidden]``."""
+    _need(x, "x", torch.float32)
+    _need(row, "row", torch.float32)
+    if row.numel() != x.shape[1]:
+        raise KernelError("add_row_: the row does not fit")
+    _done(_lib().oxr_add_row_f32(x.data_ptr(), row.data_ptr(), x.shape[0], x.shape[1], _stream()), "add_row")
+    return x
+
+
+def clamped_glu(gate_up: torch.Tensor, *, alpha: float, limit: float, interleave: int = 0) -> torch.Tensor:
+    """``g * sigmoid(alpha g) * (u + 1)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)`` for ``gate_up = [gate | up]``
+    along the last axis (or alternating in groups of ``interleave`` columns)."""
+    _need(gate_up, "gate_up")
+    n, two_i = gate_up.shape
+    if two_i % 2:
+        raise KernelError("gate_up must have an even number of columns")
+    out = torch.empty((n, two_i // 2), dtype=gate_up.dtype, device=gate_up.device)
+    _done(_lib().oxr_clamped_glu(out.data_ptr(), gate_up.data_ptr(), n, two_i // 2, int(interleave), float(alpha), float(limit), _dtype_code(gate_up),
+                                 _stream()), "clamped_glu")
+    return out
+
+
+def rotary_angles(positions: torch.Tensor, freq: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """fp32 ``cos`` and ``sin`` ``[tokens, len(freq)]`` of ``position * freq[i]`` for this step's tokens; the product and the functions are
+    evaluated in fp64 (``freq`` is a float64 device tensor) and rounded once, so the table is exact to fp32 at any position."""
+    _need(positions, "positions", torch.int32)
+    _need(freq, "freq", torch.float64)
+    n, half = positions.numel(), freq.numel()
+    cos = torch.empty((n, half), dtype=torch.float32, device=positions.device)
+    sin = torch.empty_like(cos)
+    _done(_lib().oxr_rotary_angles(cos.data_ptr(), sin.data_ptr(), positions.data_ptr(), freq.data_ptr(), n, half, _stream()), "rotary_angles")
+    return cos, sin
+
+
+# --------------------------------------------------------------------------------------------------- Mamba-2
+def mamba_conv(proj: torch.Tensor, col0: int, channels: int, weight: torch.Tensor, bias: torch.Tensor, tail: torch.Tensor, *, req_of_token: torch.Tensor,
+               cu_q: torch.Tensor, state_slots: torch.Tensor, n_requests: int) -> torch.Tensor:
+    """Causal per-channel convolution with SiLU over columns ``[col0, col0 + channels)`` of ``proj`` for a packed step; ``tail``
+    ``[slots, ...]`` (fp32, a view whose first axis is the slot) holds each request's last ``taps - 1`` inputs and is rolled forward."""
+    _need(proj, "proj")
+    _need(weight, "conv weight", torch.float32)
+    _need(bias, "conv bias", torch.float32)
+    if tail.dtype != torch.float32 or tail.stride(-1) != 1:
+        raise KernelError("mamba_conv: the tail must be fp32 with a dense last axis")
+    n = proj.shape[0]
+    taps = weight.shape[1]
+    out = torch.empty((n, channels), dtype=proj.dtype, device=proj.device)
+    _done(_lib().oxr_mamba_conv(out.data_ptr(), proj.data_ptr(), n, n_requests, proj.shape[1], col0, channels, taps, weight.data_ptr(), bias.data_ptr(),
+                                tail.data_ptr(), tail.stride(0), req_of_token.data_ptr(), cu_q.data_ptr(), state_slots.data_ptr(), _dtype_code(proj),
+                                _stream()), "mamba_conv")
+    return out
+
+
+def mamba_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col0: int, *, heads: int, vdim: int, state: int, groups: int, dt_bias: torch.Tensor,
+               a_log: torch.Tensor, d_skip: torch.Tensor, ssm: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, n_requests: int) -> torch.Tensor:
+    """The selective-state recurrence over a packed step: fp32 ``y [tokens, heads * vdim]``; ``ssm`` (fp32 view, first axis the slot, each
+    slot ``[heads, vdim, state]``) is read and left at the state after each request's last token."""
+    _need(xbc, "xbc")
+    _need(proj, "proj")
+    if ssm.dtype != torch.float32 or ssm.stride(-1) != 1:
+        raise KernelError("mamba_scan: the state must be fp32 with a dense last axis")
+    n = xbc.shape[0]
+    y = torch.empty((n, heads * vdim), dtype=torch.float32, device=xbc.device)
+    _done(_lib().oxr_mamba_scan(y.data_ptr(), xbc.data_ptr(), proj.data_ptr(), n_requests, proj.shape[1], dt_col0, heads, vdim, state, groups,
+                                dt_bias.data_ptr(), a_log.data_ptr(), d_skip.data_ptr(), ssm.data_ptr(), ssm.stride(0), cu_q.data_ptr(),
+                                state_slots.data_ptr(), _dtype_code(xbc), _stream()), "mamba_scan")
+    return y
+
+
+def gated_group_norm(y: torch.Tensor, proj: torch.Tensor, z_col0: int, weight: torch.Tensor, parts: int, eps: float) -> torch.Tensor:
+    """``v = y * silu(z)`` with z the columns ``[z_col0, z_col0 + inner)`` of ``proj``; each of ``parts`` equal stretches of ``v`` is divided by
+    its own root mean square, times ``weight``; rounded to ``proj.dtype``."""
+    _need(y, "y", torch.float32)
+    _need(proj, "proj")
+    _need(weight, "weight", torch.float32)
+    n, inner = y.shape
+    out = torch.empty((n, inner), dtype=proj.dtype, device=y.device)
+    _done(_lib().oxr_gated_group_norm(out.data_ptr(), y.data_ptr(), proj.data_ptr(), n, proj.shape[1], z_col0, weight.data_ptr(), inner, parts,
+                                      float(eps), _dtype_code(proj), _stream()), "gated_group_norm")
+    return out
+
+
+# --------------------------------------------------------------------------------------------------- attention with mask and sizes as arguments
+def scatter_rows(pool: torch.Tensor, src: torch.Tensor, col0: int, width: int, slots: torch.Tensor, status: torch.Tensor) -> None:
+    """``pool[slots[t]] = src[t, col0 : col0 + width]`` for a pool ``[pages, page_size, ...]`` whose slot rows hold ``width`` values; slot -1 skips."""
+    _need(pool, "pool")
+    _need(src, "src", pool.dtype)
+    n_slots = pool.shape[0] * pool.shape[1]
+    row = pool[0, 0].numel()
+    if width != row:
+        raise KernelError(f"scatter_rows: a slot holds {row} values, the source brings {width}")
+    _done(_lib().oxr_scatter_rows(pool.data_ptr(), row, n_slots, src.data_ptr(), src.shape[1], col0, width, slots.data_ptr(), src.shape[0],
+                                  _dtype_code(src), status.data_ptr(), _stream()), "scatter_rows")
+
+
+def latent_prep(pool: torch.Tensor, down: torch.Tensor, rank: int, rot: int, weight: torch.Tensor, eps: float, q: torch.Tensor, heads: int,
+                q_head_dim: int, q_rot0: int, q_out: torch.Tensor, qo_head_dim: int, qo_rot0: int, cos: torch.Tensor, sin: torch.Tensor,
+                slots: torch.Tensor, status: torch.Tensor) -> None:
+    """Per token: the latent cache row ``[rmsnorm(down[:rank]) * weight | rotate(down[rank:])]`` goes to ``pool[slot]`` (slot -1: not stored), and
+    every head's rotated query part ``rotate(q[h, q_rot0 : q_rot0 + rot])`` to ``q_out[h, qo_rot0 : ...]``. ``rotate`` turns entry pairs (2i, 2i+1)
+    by the token's angle i (``cos``/``sin`` ``[tokens, half]``); entries past ``2 * half`` pass unchanged."""
+    _need(pool, "pool")
+    _need(down, "down", pool.dtype)
+    _need(q, "q", pool.dtype)
+    _need(q_out, "q_out", pool.dtype)
+    _need(cos, "cos", torch.float32)
+    n = down.shape[0]
+    if down.shape[1] != rank + rot or pool[0, 0].numel() != rank + rot:
+        raise KernelError("latent_prep: sizes of the down projection and the pool do not fit")
+    _done(_lib().oxr_latent_prep(pool.data_ptr(), rank + rot, pool.shape[0] * pool.shape[1], down.data_ptr(), rank, rot, weight.data_ptr(), float(eps),
+                                 q.data_ptr(), heads, q_head_dim, q_rot0, q_out.data_ptr(), qo_head_dim, qo_rot0, cos.data_ptr(), sin.data_ptr(),
+                                 cos.shape[1], slots.data_ptr(), n, _dtype_code(down), status.data_ptr(), _stream()), "latent_prep")
+
+
+def head_linear(out: torch.Tensor, out0: int, x: torch.Tensor, x0: int, weight: torch.Tensor) -> torch.Tensor:
+    """``out[t, h, out0 : out0 + n_out] = x[t, h, x0 : x0 + n_in] @ weight[h]`` for ``weight [heads, n_in, n_out]``; ``x`` and ``out`` are
+    ``[tokens, heads, *]``; fp32 sums."""
+    _need(out, "out")
+    _need(x, "x", out.dtype)
+    _need(weight, "weight", out.dtype)
+    heads, n_in, n_out = weight.shape
+    n = x.shape[0]
+    if x.shape[1] != heads or out.shape[1] != heads or x0 + n_in > x.shape[2] or out0 + n_out > out.shape[2]:
+        raise KernelError("head_linear: sizes do not fit")
+    _done(_lib().oxr_head_linear(out.data_ptr(), out.shape[2], out0, x.data_ptr(), x.shape[2], x0, weight.data_ptr(), n_in, n_out, heads, n,
+                                 _dtype_code(x), _stream()), "head_linear")
+    return out
+
+
+def attention_rows(q: torch.Tensor, num_heads: int, k_pool: torch.Tensor, v_pool: torch.Tensor | None, *, value_dim: int, positions: torch.Tensor,
+                   req_of_token: torch.Tensor, block_table: torch.Tensor, scale: float, chunk: int = 0, window: int = 0,
+                   dist_bias: torch.Tensor | None = None, sink: torch.Tensor | None = None, status: torch.Tensor) -> torch.Tensor:
+    """Attention of the step's tokens over the paged cache with the mask and every size as an argument, in fp32 arithmetic.
+
+    ``q [tokens, >= H * DK]``: the queries are the first ``H * DK`` columns (so a stacked q|k|v product can be handed over as it is);
+    ``k_pool [pages, page_size, KV, DK]``; ``v_pool [pages, page_size, KV, DV]`` or None, when the values are the first ``value_dim`` entries
+    of the key rows (a latent cache). Token t at position p of its request sees keys j <= p, within its chunk of ``chunk`` positions
+    (counted from 0) and within its last ``window`` keys when those are given. ``dist_bias [rows, H]`` (fp32) is added to the scaled score by
+    distance p - j (the last row for all larger ones); ``sink [H]`` adds ``exp(sink)`` to the softmax denominator.
+    Returns ``[tokens, H * value_dim]``."""
+    _need(q, "q")
+    _need(k_pool, "k_pool", q.dtype)
+    n, H = q.shape[0], int(num_heads)
+    pages, page_size, KV, DK = k_pool.shape
+    if q.dim() != 2 or q.shape[1] < H * DK:
+        raise KernelError(f"attention_rows: {H} heads of {DK} do not fit rows of {tuple(q.shape)}")
+    if v_pool is None:
+        v, v_slot, v_head = k_pool, KV * DK, DK
+        if value_dim > DK:
+            raise KernelError("attention_rows: values read from key rows cannot be wider than the keys")
+    else:
+        _need(v_pool, "v_pool", q.dtype)
+        if v_pool.shape[:3] != k_pool.shape[:3] or v_pool.shape[3] != value_dim:
+            raise KernelError("attention_rows: the value pool does not fit the key pool")
+        v, v_slot, v_head = v_pool, KV * value_dim, value_dim
+    bias_rows = 0
+    if dist_bias is not None:
+        _need(dist_bias, "dist_bias", torch.float32)
+        if dist_bias.dim() != 2 or dist_bias.shape[1] != H:
+            raise KernelError("attention_rows: the distance bias must be [rows, heads]")
+        bias_rows = dist_bias.shape[0]
+    if sink is not None:
+        _need(sink, "sink", torch.float32)
+    out = torch.empty((n, H * value_dim), dtype=q.dtype, device=q.device)
+    _done(_lib().oxr_attention_rows(out.data_ptr(), q.data_ptr(), q.shape[1], k_pool.data_ptr(), KV * DK, DK, v.data_ptr(), v_slot, v_head, DK, value_dim, H,
+                                    KV, n, positions.data_ptr(), req_of_token.data_ptr(), block_table.data_ptr(), block_table.shape[1], page_size, pages,
+                                    float(scale), int(chunk), int(window), _ptr(dist_bias), bias_rows, _ptr(sink), _dtype_code(q), status.data_ptr(),
+                                    _stream()), "attention_rows")
+    return out

@@ -57,6 +57,9 @@ class GroupedQueryAttention(Mixer):
     def cache_need(self) -> PagedKVNeed:
         return PagedKVNeed(self.KV, self.D, self.window)
 
+    def kernel_head_dims(self) -> tuple[int, ...]:
+        return (self.D,)
+
     def tile_specs(self) -> list[tuple[int, int, int]]:
         return ops.attention_tile_specs(self.H, self.KV, self.D, self.runtime.dtype, self.runtime.page_size)
 

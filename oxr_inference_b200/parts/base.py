@@ -79,6 +79,16 @@ class PagedKVNeed:
     head_dim: int
     window: int = 0
     """0: all keys are kept; > 0: a query sees its last ``window`` keys, pages wholly behind that are released."""
+    value_dim: int | None = None
+    """Size of a value row: None = ``head_dim``; 0 = no value pool at all (the values are read from the key rows, as with a latent
+    cache that keeps one shared row per token)."""
+    chunk: int = 0
+    """> 0: a query sees only keys of its own chunk of that many positions (counted from 0); pages wholly before the chunk of the next
+    query are released."""
+
+    @property
+    def v_dim(self) -> int:
+        return self.head_dim if self.value_dim is None else self.value_dim
 
 
 @dataclass(frozen=True)
@@ -145,6 +155,8 @@ class StepContext:
     status: torch.Tensor | None = None
     sampling: dict[str, torch.Tensor] = field(default_factory=dict)
     """Per logit row: temperature (fp32), seed_lo, seed_hi, counter, row_slot (the row's state slot)."""
+    shared: dict = field(default_factory=dict)
+    """What parts compute once per step and share between layers (rotary angles of the step's tokens); emptied when a step begins."""
 
     @property
     def single_tokens(self) -> bool:
@@ -208,6 +220,10 @@ class Mixer(Part):
         the requests the list covers)."""
         return []
 
+    def kernel_head_dims(self) -> tuple[int, ...]:
+        """Head sizes for which this mixer needs the attention library that is compiled per head size."""
+        return ()
+
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         raise NotImplementedError
 
@@ -225,6 +241,14 @@ class FeedForward(Part):
     def forward_deferred(self, h: torch.Tensor) -> "torch.Tensor | DeferredLinear":
         """``forward`` with the last projection left to the caller where the part ends in one (optional to override)."""
         return self.forward(h)
+
+
+class Joint(Part):
+    """A map of the whole fp32 stream between two layer runs: ``forward(stream, first, arg, ctx) -> stream`` where ``first`` is the
+    embedding's output (never written to) and ``arg`` comes from the schedule entry."""
+
+    def forward(self, stream: torch.Tensor, first: torch.Tensor, arg: int, ctx: "StepContext") -> torch.Tensor:
+        raise NotImplementedError
 
 
 class Embedding(Part):
@@ -276,3 +300,4 @@ FEED_FORWARDS = Registry("feed-forward")
 ARRANGEMENTS = Registry("block arrangement")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("output head")
+JOINTS = Registry("joint")

@@ -50,3 +50,46 @@ class PreNormBlock:
             a = self.mixer.forward(h, ctx, cache)
         h, residual = self._norm(self.feed_forward_norm, a, residual, self.feed_forward)
         return (self.feed_forward.forward_deferred(h) if defer_output else self.feed_forward.forward(h)), residual
+
+
+@ARRANGEMENTS.register("sandwich_norm")
+class SandwichNormBlock:
+    """``x += post_norm(mixer(pre_norm(x)))`` and, when the block has a feed-forward, ``x += post_norm(ff(pre_norm(x)))``: a norm on
+    both sides of each sublayer. Nothing can stay pending between sublayers (the output is normalised before it is added), so the
+    fp32 stream is kept whole: ``forward`` takes it in ``residual`` (or, for the first block, in ``x``), updates it in place and
+    returns ``(None, stream)``. The post-norm, the add and the pre-norm that follows inside the block are one kernel."""
+
+    supports_deferred = False
+    accepts_deferred_input = False
+
+    def __init__(self, mixer: Mixer, mixer_norm: Norm, feed_forward: FeedForward | None, feed_forward_norm: Norm | None, *,
+                 mixer_post_norm: Norm, feed_forward_post_norm: Norm | None = None):
+        if (feed_forward is None) != (feed_forward_norm is None) or (feed_forward is None) != (feed_forward_post_norm is None):
+            raise ValueError("a feed-forward comes with both of its norms or not at all")
+        self.mixer, self.mixer_norm, self.mixer_post_norm = mixer, mixer_norm, mixer_post_norm
+        self.feed_forward, self.feed_forward_norm, self.feed_forward_post_norm = feed_forward, feed_forward_norm, feed_forward_post_norm
+
+    def parts(self) -> dict[str, object]:
+        out = {"mixer": self.mixer, "mixer_norm": self.mixer_norm, "mixer_post_norm": self.mixer_post_norm}
+        if self.feed_forward is not None:
+            out.update(feed_forward=self.feed_forward, feed_forward_norm=self.feed_forward_norm, feed_forward_post_norm=self.feed_forward_post_norm)
+        return out
+
+    def forward(self, x, residual: torch.Tensor | None, ctx: StepContext, cache: LayerCache, defer_output: bool = False):
+        if residual is None:
+            if isinstance(x, DeferredLinear):
+                x = x.materialize()
+            if x.dtype != torch.float32:
+                raise ValueError("this arrangement keeps the stream in fp32: the embedding must hand it over whole")
+            stream = x
+        elif x is not None:
+            raise ValueError("this arrangement takes the stream whole; the block before it left an output that is not yet added")
+        else:
+            stream = residual
+        a = self.mixer.forward(self.mixer_norm.stream_norm(stream), ctx, cache)
+        if self.feed_forward is None:
+            self.mixer_post_norm.add_normed(stream, a)
+            return None, stream
+        h = self.mixer_post_norm.add_normed(stream, a, then=self.feed_forward_norm)
+        self.feed_forward_post_norm.add_normed(stream, self.feed_forward.forward(h))
+        return None, stream

@@ -8,17 +8,20 @@ import torch
 
 from oxr_inference_b200 import ops
 from oxr_inference_b200.cache.plan import CachePlan, make_cache_plan
-from oxr_inference_b200.parts.base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS,
+from oxr_inference_b200.parts.base import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, JOINTS, MIXERS, NORMS, POSITION_ENCODINGS,
                                            Embedding, Head, ParamInfo, Part, Runtime, StepContext)
 from oxr_inference_b200.parts.spec import ModelSpec, PartSpec
 
 
 @EMBEDDINGS.register("token_embedding")
 class TokenEmbedding(Embedding):
-    """``x = table[ids]`` (oxr_runtime/language.py:155, oxr_runtime/decode_graph.py:75)."""
+    """``x = table[ids] * scale`` (oxr_runtime/language.py:155, oxr_runtime/decode_graph.py:75; the reference has no scale).
+    ``whole_stream``: the output is the fp32 residual stream itself (for blocks that keep the stream whole) instead of
+    activations that the first norm turns into one."""
 
-    def __init__(self, runtime: Runtime, *, vocab_size: int, hidden_size: int):
+    def __init__(self, runtime: Runtime, *, vocab_size: int, hidden_size: int, scale: float = 1.0, whole_stream: bool = False):
         self.runtime, self.vocab, self.hidden = runtime, int(vocab_size), int(hidden_size)
+        self.scale, self.whole_stream = float(scale), bool(whole_stream)
         self.weight: torch.Tensor | None = None
 
     def parameters(self) -> dict[str, ParamInfo]:
@@ -31,7 +34,7 @@ class TokenEmbedding(Embedding):
         self.weight = tensor.to(device=self.runtime.device, dtype=dtype).contiguous()
 
     def forward(self, ids: torch.Tensor) -> torch.Tensor:
-        return ops.embedding(ids, self.weight, self.runtime.dtype, self.runtime.status)
+        return ops.embedding(ids, self.weight, torch.float32 if self.whole_stream else self.runtime.dtype, self.runtime.status, self.scale)
 
 
 @HEADS.register("linear_head")
@@ -65,28 +68,41 @@ class DecoderModel:
         self._positions: dict[tuple, Any] = {}
 
         self.embedding = EMBEDDINGS.build(spec.embedding.kind, runtime, **spec.embedding.params)
-        self._register(self.embedding, spec.embedding.prefix)
+        self._register(self.embedding, spec.embedding)
 
         self.blocks = []
         for layer in spec.layers:
             position = self._position(layer.position)
             mixer = MIXERS.build(layer.mixer.kind, runtime, position, **layer.mixer.params)
             mixer_norm = NORMS.build(layer.mixer_norm.kind, runtime, **layer.mixer_norm.params)
-            ff = FEED_FORWARDS.build(layer.feed_forward.kind, runtime, **layer.feed_forward.params)
-            ff_norm = NORMS.build(layer.feed_forward_norm.kind, runtime, **layer.feed_forward_norm.params)
-            self.blocks.append(ARRANGEMENTS.build(layer.arrangement, mixer, mixer_norm, ff, ff_norm))
-            for part, part_spec in ((mixer, layer.mixer), (mixer_norm, layer.mixer_norm), (ff, layer.feed_forward),
-                                    (ff_norm, layer.feed_forward_norm)):
-                self._register(part, part_spec.prefix)
+            ff = FEED_FORWARDS.build(layer.feed_forward.kind, runtime, **layer.feed_forward.params) if layer.feed_forward else None
+            ff_norm = NORMS.build(layer.feed_forward_norm.kind, runtime, **layer.feed_forward_norm.params) if layer.feed_forward_norm else None
+            made = [(mixer, layer.mixer), (mixer_norm, layer.mixer_norm), (ff, layer.feed_forward), (ff_norm, layer.feed_forward_norm)]
+            post = {}
+            for key, post_spec in (("mixer_post_norm", layer.mixer_post_norm), ("feed_forward_post_norm", layer.feed_forward_post_norm)):
+                if post_spec is not None:
+                    post[key] = NORMS.build(post_spec.kind, runtime, **post_spec.params)
+                    made.append((post[key], post_spec))
+            self.blocks.append(ARRANGEMENTS.build(layer.arrangement, mixer, mixer_norm, ff, ff_norm, **post))
+            for part, part_spec in made:
+                if part is not None:
+                    self._register(part, part_spec)
+
+        self.joints = []
+        for joint_spec in spec.joints:
+            self.joints.append(JOINTS.build(joint_spec.kind, runtime, **joint_spec.params))
+            self._register(self.joints[-1], joint_spec)
 
         self.final_norm = NORMS.build(spec.final_norm.kind, runtime, **spec.final_norm.params)
-        self._register(self.final_norm, spec.final_norm.prefix)
+        self._register(self.final_norm, spec.final_norm)
         self.head = HEADS.build(spec.head.kind, runtime, self.embedding, **spec.head.params)
-        self._register(self.head, spec.head.prefix)
+        self._register(self.head, spec.head)
 
         for i, entry in enumerate(spec.schedule):
             if not 0 <= entry.layer < len(self.blocks):
                 raise ValueError(f"schedule entry {i} names layer {entry.layer}; the model has {len(self.blocks)}")
+            if entry.joint is not None and not 0 <= entry.joint < len(self.joints):
+                raise ValueError(f"schedule entry {i} names joint {entry.joint}; the model has {len(self.joints)}")
         self.schedule = spec.schedule
         self.cache_plan: CachePlan = make_cache_plan(
             [self.blocks[e.layer].mixer.cache_need() for e in self.schedule], [e.cache_of for e in self.schedule])
@@ -101,9 +117,9 @@ class DecoderModel:
             self._positions[key] = POSITION_ENCODINGS.build(spec.kind, self.runtime, **spec.params)
         return self._positions[key]
 
-    def _register(self, part: Part, prefix: str) -> None:
+    def _register(self, part: Part, spec: PartSpec) -> None:
         for local, info in part.parameters().items():
-            name = prefix + local
+            name = spec.prefix + spec.names.get(local, local)
             if name in self._named:
                 raise ValueError(f"two parts claim the tensor {name!r}")
             self._named[name] = (part, local, info)
@@ -121,15 +137,27 @@ class DecoderModel:
         return out
 
     def head_dims(self) -> tuple[int, ...]:
-        return tuple(sorted({g.need.head_dim for g in self.cache_plan.groups}))
+        """Head sizes whose per-size attention library this model's mixers run."""
+        return tuple(sorted({d for b in self.blocks for d in b.mixer.kernel_head_dims()}))
 
     # ---- the forward pass of one step
     def step(self, ctx: StepContext, cache) -> torch.Tensor:
         """Run the step's tokens through every scheduled block; fp32 logits ``[len(ctx.logit_rows), vocab]``."""
+        ctx.shared.clear()
         x = self.embedding.forward(ctx.token_ids)
         residual = None
+        first = None
+        if self.joints:
+            # joints read the embedding's output again later: blocks that keep the stream whole write into their own copy
+            first, x = x, x.clone()
         for pos, entry in enumerate(self.schedule):
             block = self.blocks[entry.layer]
+            if entry.joint is not None:
+                if residual is None:
+                    x, residual = None, x
+                elif x is not None:
+                    raise ValueError("a joint needs the stream whole: the block before it left an output that is not yet added")
+                residual = self.joints[entry.joint].forward(residual, first, entry.joint_arg, ctx)
             # a block may leave its last projection to the next block's norm, if both sides say that they can
             after = self.blocks[self.schedule[pos + 1].layer] if pos + 1 < len(self.schedule) else None
             if getattr(block, "supports_deferred", False) and getattr(after, "accepts_deferred_input", False):
@@ -138,5 +166,8 @@ class DecoderModel:
                 x, residual = block.forward(x, residual, ctx, cache.layer_cache(pos, ctx))
         if ctx.logit_rows.numel() == 0:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.runtime.device)
-        h = self.final_norm.forward_rows(x, residual, ctx.logit_rows)
+        if x is None:   # the blocks kept the stream whole
+            h = self.final_norm.stream_rows(residual, ctx.logit_rows)
+        else:
+            h = self.final_norm.forward_rows(x, residual, ctx.logit_rows)
         return self.head.forward(h)

@@ -1,0 +1,173 @@
+"""Attention mixers whose mask, sizes and extras are arguments: grouped-query attention within chunks with a bias by distance,
+and latent attention (one compressed row per token that serves as key and value of every head) with a softmax sink."""
+
+from __future__ import annotations
+
+import math
+
+import torch
+
+from oxr_inference_b200 import ops
+from oxr_inference_b200.parts.base import MIXERS, LayerCache, Mixer, PagedKVNeed, ParamInfo, PositionEncoding, Runtime, StepContext
+from oxr_inference_b200.parts.linear import StackedLinear
+
+
+def distance_bucket(n: int, rows: int, far: float) -> int:
+    """Row of a ``rows``-row bias table for a key ``n`` positions back: one row per distance below ``rows // 2``, then rows spaced
+    evenly in the logarithm of the distance up to ``far``; everything at or beyond ``far`` shares the last row."""
+    half = rows // 2
+    if n < half:
+        return n
+    return min(rows - 1, half + int(math.floor(math.log(n / half) / math.log(far / half) * (rows - half))))
+
+
+def bias_by_distance(table: torch.Tensor, far: float) -> torch.Tensor:
+    """Expand a bucketed bias table ``[rows, heads]`` into one row per distance ``0 .. ceil(far)``; the last row stands for every
+    larger distance (all of them fall into the last bucket). The buckets are worked out on the host in double precision, once."""
+    rows = table.shape[0]
+    half = rows // 2
+    if rows < 2 or far <= half:
+        raise ValueError(f"a distance-bias table of {rows} rows needs its far distance ({far}) beyond {half}")
+    last = max(half, int(math.ceil(far)))
+    index = [distance_bucket(n, rows, far) for n in range(last + 1)]
+    if index[-1] != rows - 1:
+        raise ValueError("the far distance does not reach the table's last row")
+    return table[torch.tensor(index, device=table.device)].contiguous()
+
+
+@MIXERS.register("masked_attention")
+class MaskedAttention(Mixer):
+    """``q, k, v = h W^T`` (no biases, no rotation) -> K and V into the paged cache -> softmax attention of each new token over the
+    keys it sees -> ``W_o``. Query head h reads key/value head ``h // (heads / kv_heads)``; keys have ``key_dim`` entries, values
+    ``value_dim``. ``chunk`` > 0: position i sees j <= i only inside its own chunk of that many positions, counted from 0 (not from
+    where a prompt was cut). ``window`` > 0: only the last ``window`` keys. ``bias_rows`` > 0: a learned table ``rel [bias_rows, heads]``
+    is added to the scaled score by bucketed distance (:func:`distance_bucket`, ``bias_far``)."""
+
+    def __init__(self, runtime: Runtime, position: PositionEncoding | None, *, hidden_size: int, num_heads: int, num_kv_heads: int, key_dim: int,
+                 value_dim: int, scale: float, chunk: int = 0, window: int = 0, bias_rows: int = 0, bias_far: float = 0.0):
+        if position is not None:
+            raise ValueError("masked_attention takes no position encoding: positions enter through its mask and bias")
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} heads are not a multiple of {num_kv_heads} KV heads")
+        self.runtime = runtime
+        self.hidden, self.H, self.KV, self.DK, self.DV = int(hidden_size), int(num_heads), int(num_kv_heads), int(key_dim), int(value_dim)
+        self.scale, self.chunk, self.window = float(scale), int(chunk), int(window)
+        self.bias_rows, self.bias_far = int(bias_rows), float(bias_far)
+        self.qkv = StackedLinear(runtime, self.hidden, {"q": self.H * self.DK, "k": self.KV * self.DK, "v": self.KV * self.DV})
+        self.out = StackedLinear(runtime, self.H * self.DV, {"o": self.hidden})
+        self.rel: torch.Tensor | None = None
+        self.dist_bias: torch.Tensor | None = None
+
+    def parameters(self) -> dict[str, ParamInfo]:
+        out = {**self.qkv.parameters(), **self.out.parameters()}
+        if self.bias_rows:
+            out["rel"] = ParamInfo((self.bias_rows, self.H), role="vector")
+        return out
+
+    def assign(self, name: str, tensor: torch.Tensor) -> None:
+        if name in self.qkv.outs:
+            self.qkv.assign(name, tensor)
+        elif name in self.out.outs:
+            self.out.assign(name, tensor)
+        elif name == "rel" and self.bias_rows:
+            self.rel = tensor.to(device=self.runtime.device, dtype=torch.float32).contiguous()
+        else:
+            raise KeyError(name)
+
+    def finish_loading(self) -> None:
+        if self.rel is not None:
+            self.dist_bias = bias_by_distance(self.rel, self.bias_far)
+
+    def cache_need(self) -> PagedKVNeed:
+        return PagedKVNeed(self.KV, self.DK, self.window, value_dim=self.DV, chunk=self.chunk)
+
+    def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        group = cache.group
+        k_pool, v_pool = group.k_pool[cache.layer_in_group], group.v_pool[cache.layer_in_group]
+        qkv = self.qkv(h)
+        if qkv.dtype != k_pool.dtype:
+            qkv = ops.cast(qkv, k_pool.dtype)
+        if cache.store:
+            q_cols, k_cols = self.H * self.DK, self.KV * self.DK
+            ops.scatter_rows(k_pool, qkv, q_cols, k_cols, group.slots, ctx.status)
+            ops.scatter_rows(v_pool, qkv, q_cols + k_cols, self.KV * self.DV, group.slots, ctx.status)
+        o = ops.attention_rows(qkv, self.H, k_pool, v_pool, value_dim=self.DV, positions=ctx.positions, req_of_token=ctx.req_of_token,
+                               block_table=group.block_table, scale=self.scale, chunk=self.chunk, window=self.window,
+                               dist_bias=self.dist_bias, status=ctx.status)
+        return self.out(o)
+
+
+@MIXERS.register("latent_attention")
+class LatentAttention(Mixer):
+    """Attention over a compressed cache. Per token ``W_dkv h`` gives ``rank`` entries that are RMS-normed (weight ``dkv.norm``) into
+    the latent ``c`` and ``rot_dim`` more that are rotated into a key part shared by all heads; only ``[c | rotated part]`` is
+    cached. Per head the unrotated key is ``W_uk c`` and the value ``W_uv c``; the query ``W_q h`` is laid out head by head as
+    ``[key_dim unrotated | rot_dim rotated]``; the score is ``(q_u . k_u + q_r . k_r) * scale``; causal; optional ``sink``: a learned
+    number per head whose exponential joins the softmax denominator (it has no key, no value and is not scaled).
+
+    Computed in the absorbed form, which never builds per-head keys or values: ``q_u . (W_uk c) = (W_uk^T q_u) . c``, so every head
+    attends with the query ``[W_uk^T q_u | q_r]`` over the one cached row per token (whose first ``rank`` entries are the value as
+    well), and ``W_uv`` is applied to the attention's output."""
+
+    def __init__(self, runtime: Runtime, position: PositionEncoding | None, *, hidden_size: int, num_heads: int, key_dim: int, rot_dim: int,
+                 value_dim: int, rank: int, scale: float, eps: float, sink: bool = True):
+        if rot_dim and position is None:
+            raise ValueError("latent_attention with a rotated part needs a position encoding")
+        self.runtime, self.position = runtime, position
+        self.hidden, self.H, self.D, self.R, self.DV, self.L = int(hidden_size), int(num_heads), int(key_dim), int(rot_dim), int(value_dim), int(rank)
+        self.scale, self.eps, self.has_sink = float(scale), float(eps), bool(sink)
+        self.q_dkv = StackedLinear(runtime, self.hidden, {"q": self.H * (self.D + self.R), "dkv": self.L + self.R})
+        self.out = StackedLinear(runtime, self.H * self.DV, {"o": self.hidden})
+        self.c_norm: torch.Tensor | None = None
+        self.sink: torch.Tensor | None = None
+        self.uk: torch.Tensor | None = None   # [H, D, L]: W_uk head by head, input-major for q_u -> latent space
+        self.uv: torch.Tensor | None = None   # [H, L, DV]: W_uv^T head by head
+
+    def parameters(self) -> dict[str, ParamInfo]:
+        out = {**self.q_dkv.parameters(), **self.out.parameters(),
+               "dkv.norm": ParamInfo((self.L,), init="around_one", role="vector"),
+               "uk": ParamInfo((self.H * self.D, self.L)), "uv": ParamInfo((self.H * self.DV, self.L))}
+        if self.has_sink:
+            out["sink"] = ParamInfo((self.H,), role="vector")
+        return out
+
+    def assign(self, name: str, tensor: torch.Tensor) -> None:
+        rt = self.runtime
+        if name in self.q_dkv.outs:
+            self.q_dkv.assign(name, tensor)
+        elif name in self.out.outs:
+            self.out.assign(name, tensor)
+        elif name == "dkv.norm":
+            self.c_norm = tensor.to(device=rt.device, dtype=torch.float32).contiguous()
+        elif name == "sink" and self.has_sink:
+            self.sink = tensor.to(device=rt.device, dtype=torch.float32).contiguous()
+        elif name == "uk":
+            self.uk = tensor.to(device=rt.device, dtype=rt.dtype).view(self.H, self.D, self.L).contiguous()
+        elif name == "uv":
+            self.uv = tensor.to(device=rt.device, dtype=rt.dtype).view(self.H, self.DV, self.L).transpose(1, 2).contiguous()
+        else:
+            raise KeyError(name)
+
+    def cache_need(self) -> PagedKVNeed:
+        return PagedKVNeed(1, self.L + self.R, 0, value_dim=0)
+
+    def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        group = cache.group
+        pool = group.k_pool[cache.layer_in_group]
+        n, H, D, R, L = ctx.n_tokens, self.H, self.D, self.R, self.L
+        both = self.q_dkv(h)
+        if both.dtype != pool.dtype:
+            both = ops.cast(both, pool.dtype)
+        q_cols = H * (D + R)
+        q = both[:, :q_cols].contiguous().view(n, H, D + R)
+        down = both[:, q_cols:].contiguous()
+        cos, sin = self.position.step_angles(ctx)
+        q_abs = torch.empty((n, H, L + R), dtype=pool.dtype, device=pool.device)
+        ops.latent_prep(pool, down, L, R, self.c_norm, self.eps, q, H, D + R, D, q_abs, L + R, L, cos, sin,
+                        group.slots if cache.store else ctx.no_store_slots, ctx.status)
+        ops.head_linear(q_abs, 0, q, 0, self.uk)
+        o_lat = ops.attention_rows(q_abs.view(n, H * (L + R)), H, pool, None, value_dim=L, positions=ctx.positions, req_of_token=ctx.req_of_token,
+                                   block_table=group.block_table, scale=self.scale, sink=self.sink, status=ctx.status)
+        o = torch.empty((n, H, self.DV), dtype=pool.dtype, device=pool.device)
+        ops.head_linear(o, 0, o_lat.view(n, H, L), 0, self.uv)
+        return self.out(o.view(n, H * self.DV))

@@ -43,3 +43,29 @@ class SwiGLU(FeedForward):
 
     def _gated(self, h: torch.Tensor) -> torch.Tensor:
         return ops.gated_silu_linear(h, self.gate_up.weight, self.gate_up.interleave)
+
+
+@FEED_FORWARDS.register("clamped_glu")
+class ClampedGLU(FeedForward):
+    """``down( g sigmoid(alpha g) (u + 1) )`` with ``g = min(h W_gate^T, limit)`` and ``u = clamp(h W_up^T, -limit, limit)``: a gated unit
+    whose gate is a sigmoid-approximated GELU (``alpha`` = 1.702), whose linear branch is shifted by one and whose two branches are
+    clamped. Gate and up are one product."""
+
+    def __init__(self, runtime: Runtime, *, hidden_size: int, intermediate_size: int, limit: float, alpha: float = 1.702):
+        self.hidden, self.inter, self.limit, self.alpha = int(hidden_size), int(intermediate_size), float(limit), float(alpha)
+        self.gate_up = StackedLinear(runtime, self.hidden, {"gate": self.inter, "up": self.inter})
+        self.down = StackedLinear(runtime, self.inter, {"down": self.hidden})
+
+    def parameters(self) -> dict[str, ParamInfo]:
+        return {**self.gate_up.parameters(), **self.down.parameters()}
+
+    def assign(self, name: str, tensor: torch.Tensor) -> None:
+        if name in self.gate_up.outs:
+            self.gate_up.assign(name, tensor)
+        elif name in self.down.outs:
+            self.down.assign(name, tensor)
+        else:
+            raise KeyError(name)
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        return self.down(ops.clamped_glu(self.gate_up(h), alpha=self.alpha, limit=self.limit, interleave=self.gate_up.interleave))

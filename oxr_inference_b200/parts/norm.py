@@ -45,3 +45,18 @@ class RMSNorm(Norm):
         if isinstance(x, DeferredLinear):
             x = x.materialize()
         return ops.add_rms_norm(x, residual, self.weight, self.eps, rows=rows)[0]
+
+    # ---- for blocks that keep the residual stream whole in fp32 (nothing pending between sublayers)
+    def stream_norm(self, stream: torch.Tensor) -> torch.Tensor:
+        """``rmsnorm(stream) * weight`` in the activation dtype."""
+        return ops.stream_rms_norm(stream, self.weight, self.eps, self.runtime.dtype)
+
+    def stream_rows(self, stream: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+        return ops.stream_rms_norm(stream, self.weight, self.eps, self.runtime.dtype, rows=rows)
+
+    def add_normed(self, stream: torch.Tensor, y: torch.Tensor, then: "RMSNorm | None" = None) -> torch.Tensor | None:
+        """``stream += rmsnorm(y) * weight`` in place; with ``then`` (the next sublayer's pre-norm) also returns its output, from the
+        same pass over the row."""
+        if then is None:
+            return ops.norm_add_norm(stream, y, self.weight, self.eps)
+        return ops.norm_add_norm(stream, y, self.weight, self.eps, then.weight, then.eps)

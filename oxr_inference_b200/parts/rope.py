@@ -1,10 +1,11 @@
-"""Rotary position encoding, half-split (GPT-NeoX) form."""
+"""Rotary position encodings: the half-split (GPT-NeoX) table, and per-step angles for the interleaved-pairs form."""
 
 from __future__ import annotations
 
 import torch
 
-from oxr_inference_b200.parts.base import POSITION_ENCODINGS, PositionEncoding, Runtime
+from oxr_inference_b200 import ops
+from oxr_inference_b200.parts.base import POSITION_ENCODINGS, PositionEncoding, Runtime, StepContext
 
 
 @POSITION_ENCODINGS.register("rope_neox")
@@ -28,3 +29,27 @@ class RotaryTable(PositionEncoding):
 
     def tables(self) -> tuple[torch.Tensor, torch.Tensor]:
         return self.cos, self.sin
+
+
+@POSITION_ENCODINGS.register("rope_pairs")
+class RotaryPairs(PositionEncoding):
+    """Rotary encoding of entry pairs (2i, 2i+1) of the first ``dims`` entries of a vector: the pair (u, v) at position p becomes
+    ``(u cos a - v sin a, v cos a + u sin a)`` with ``a = p * base^(-2i/dims)``. There is no table over all positions: each step
+    computes cos and sin for its own tokens, once, shared by every layer with the same ``dims`` and ``base`` (the frequencies, the
+    product with the position and the functions in fp64, rounded once to fp32), so no position limit comes from here."""
+
+    def __init__(self, runtime: Runtime, *, dims: int, base: float):
+        if dims % 2 or dims <= 0:
+            raise ValueError(f"rotary dimension {dims} must be even and positive")
+        self.dims, self.base = int(dims), float(base)
+        freq = torch.tensor([self.base ** (-2.0 * i / self.dims) for i in range(self.dims // 2)], dtype=torch.float64)
+        self.freq = freq.to(runtime.device)
+
+    def tables(self):
+        raise NotImplementedError("rope_pairs has per-step angles (step_angles), not a table over all positions")
+
+    def step_angles(self, ctx: StepContext) -> tuple[torch.Tensor, torch.Tensor]:
+        key = ("rope_pairs", self.dims, self.base)
+        if key not in ctx.shared:
+            ctx.shared[key] = ops.rotary_angles(ctx.positions, self.freq)
+        return ctx.shared[key]

@@ -18,6 +18,9 @@ class PartSpec:
     """Sizes and constants of the part; the part's constructor receives them as keyword arguments."""
     prefix: str = ""
     """Checkpoint-name prefix of the part's tensors, e.g. ``model.layers.3.self_attn.``."""
+    names: Mapping[str, str] = field(default_factory=dict)
+    """Checkpoint names (behind the prefix) of tensors that the checkpoint calls otherwise than the part does, by the part's
+    local name; ``{"weight": ""}`` makes the prefix itself the name."""
 
     def key(self) -> tuple:
         return (self.kind, tuple(sorted((k, repr(v)) for k, v in self.params.items())))
@@ -29,11 +32,15 @@ class LayerSpec:
 
     mixer: PartSpec
     mixer_norm: PartSpec
-    feed_forward: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward: PartSpec | None
+    """None: the block has the mixer's sublayer only (arrangements that allow it)."""
+    feed_forward_norm: PartSpec | None
     arrangement: str = "pre_norm"
     position: PartSpec | None = None
     """Position encoding handed to the mixer (shared between layers whose specs are equal)."""
+    mixer_post_norm: PartSpec | None = None
+    """Norm of the mixer's output before it joins the stream (arrangements with a norm on both sides of a sublayer)."""
+    feed_forward_post_norm: PartSpec | None = None
 
 
 @dataclass(frozen=True)
@@ -45,6 +52,10 @@ class ScheduleEntry:
     """Index into ``ModelSpec.layers``: whose parameters run."""
     cache_of: int | None = None
     """Schedule position whose cache this run reads instead of filling one of its own."""
+    joint: int | None = None
+    """Index into ``ModelSpec.joints``: a map of the stream that runs right before this layer run."""
+    joint_arg: int = 0
+    """Handed to the joint (which pass of a repeated stretch begins here)."""
 
 
 @dataclass(frozen=True)
@@ -62,6 +73,8 @@ class ModelSpec:
     eos_token_ids: tuple[int, ...] = ()
     ignored_tensors: tuple[str, ...] = ()
     """Checkpoint names that may be present and are not used (regular expressions)."""
+    joints: tuple[PartSpec, ...] = ()
+    """Maps of the stream between layer runs (``ScheduleEntry.joint``), e.g. the re-entry of a stretch that runs several times."""
     name_prefixes: tuple[str, ...] = ("",)
     """Prefixes under which a checkpoint may store all names (the reference's files use ``llm.``,
     oxr_runtime/weight_names.py:11)."""

@@ -52,6 +52,16 @@ def checkpoint_files(model_dir: str | Path) -> list[Path]:
     raise FileNotFoundError(f"{root} holds neither model.safetensors nor model.safetensors.index.json")
 
 
+def tensor_shapes(model_dir: str | Path) -> dict[str, tuple[int, ...]]:
+    """Name -> shape of every tensor of the checkpoint (headers only): for designs that leave a size to a tensor's shape."""
+    out: dict[str, tuple[int, ...]] = {}
+    for path in checkpoint_files(model_dir):
+        with safe_open(str(path), framework="pt", device="cpu") as f:
+            for name in f.keys():  # noqa: SIM118
+                out[name] = tuple(f.get_slice(name).get_shape())
+    return out
+
+
 def load_weights(model: DecoderModel, model_dir: str | Path) -> None:
     named = model.named_parameters()
     spec = model.spec

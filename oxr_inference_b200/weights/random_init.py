@@ -39,7 +39,7 @@ def random_tensor(name: str, info: ParamInfo, seed: int, *, std: float, norm_std
 def shape_only_model(raw_config: Mapping[str, Any]) -> DecoderModel:
     """The model's structure on the host, with no weights: enough to list tensor names and shapes."""
     arch = resolve_architecture(raw_config)
-    spec = arch.model_spec(arch.config_from_dict(raw_config, None))
+    spec = arch.spec_for(arch.config_from_dict(raw_config, None))
     cpu = torch.device("cpu")
     runtime = Runtime(device=cpu, dtype=torch.float32, max_positions=1, status=torch.zeros(4, dtype=torch.int32))
     return DecoderModel(spec, runtime)
