@@ -150,9 +150,15 @@ class CacheManager:
             return False
         for table, pool, n in zip(rc.tables, self.pools, needed):
             table.extend(pool.allocate(n))
-        rc.room = min(len(table) for table in rc.tables) * self.page_size
+        rc.room = self._room(rc)
         rc.version += 1
         return True
+
+    NO_PAGES_ROOM = 1 << 62
+    """``room`` of a request of a model that keeps no paged cache at all (fixed-size state only): never the limit."""
+
+    def _room(self, rc: RequestCache) -> int:
+        return min((len(table) for table in rc.tables), default=self.NO_PAGES_ROOM // self.page_size) * self.page_size
 
     def advance(self, rc: RequestCache, new_length: int) -> None:
         """The step ran: the request now holds ``new_length`` tokens. Pages that every later query's window has
@@ -208,7 +214,7 @@ class CacheManager:
             if len(held) + pool.free != pool.num_pages:
                 raise AssertionError(f"group {g}: {len(held)} held + {pool.free} free != {pool.num_pages}")
         for rc in self._open.values():
-            if rc.room != min(len(t) for t in rc.tables) * self.page_size:
+            if rc.room != self._room(rc) and rc.tables:
                 raise AssertionError(f"request {rc.key!r}: room {rc.room} does not match its tables")
             for g, table in enumerate(rc.tables):
                 k = rc.released[g]

@@ -269,7 +269,7 @@ class BatchBuilder:
             self._same_requests[id(device_block)] = (signature,)
             ctx = self._fixed_views.get(id(device_block))
             if ctx is None:
-                ctx = self._fixed_views[id(device_block)] = self.views(layout, device_block, tiles_n, q_lens, ctx_lens, max(layout.widths) * P)
+                ctx = self._fixed_views[id(device_block)] = self.views(layout, device_block, tiles_n, q_lens, ctx_lens, max(layout.widths, default=0) * P)
             ctx.q_lens, ctx.ctx_lens_host = q_lens, ctx_lens
             return ctx
         ctx = self.views(layout, device_block, tiles_n, q_lens, ctx_lens, max(ctx_lens))

@@ -35,7 +35,7 @@ class DecodeGraphs:
         """(batch bucket, table-width bucket, lengths uneven) of the graph that ``run`` replayed last."""
 
     def _width_bucket(self, entries: list[StepEntry]) -> int:
-        need = max(len(t) for e in entries for t in e.cache.tables)
+        need = max((len(t) for e in entries for t in e.cache.tables), default=1)
         w = 16
         while w < need:
             w *= 2

@@ -36,10 +36,6 @@ def rms_norm(x: torch.Tensor, weight: torch.Tensor | None, eps: float) -> torch.
     return y if weight is None else y * weight
 
 
-def gelu_tanh(z: torch.Tensor) -> torch.Tensor:
-    return 0.5 * z * (1 + torch.tanh(math.sqrt(2 / math.pi) * (z + 0.044715 * z ** 3)))
-
-
 def distance_bucket(n: int, rows: int, far: float) -> int:
     """Row of the distance-bias table for a key ``n`` positions back: exact below rows/2, logarithmic up to ``far``."""
     half = rows // 2
@@ -185,3 +181,17 @@ def forward(cfg: dict, w: dict, ids: list[int], trace: list | None = None) -> to
         if trace is not None:
             trace.append(x.clone())
     return rms_norm(x, w["final.norm"], eps).to(dtype) @ w["head"].T
+
+
+def greedy(cfg: dict, w: dict, prompt: list[int], n: int) -> tuple[list[int], list[float]]:
+    """``n`` greedy tokens after ``prompt`` (the whole sequence is run again for each), and for each the gap between the two
+    largest logits, so that a caller can tell a real difference from a near-tie."""
+    ids, out, gaps = list(prompt), [], []
+    for _ in range(n):
+        last = forward(cfg, w, ids)[-1]
+        top = last.topk(2).values
+        nxt = int(last.argmax())
+        gaps.append(float(top[0] - top[1]))
+        out.append(nxt)
+        ids.append(nxt)
+    return out, gaps

@@ -110,7 +110,8 @@ class Replay:
 
     def __init__(self, folder: Path, dtype: str, out: Path, max_tokens: int, page_size: int = 16, env: dict | None = None):
         self.out = out
-        self.vocab = json.loads((folder / "config.json").read_text())["vocab_size"]
+        cfg = json.loads((folder / "config.json").read_text())
+        self.vocab = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
         cmd = [sys.executable, str(ROOT / "bin" / "trace_run"), "--model", str(folder), "--dtype", dtype, "--out", str(out),
                "--max-tokens", str(max_tokens), "--page-size", str(page_size)]
         self.proc = subprocess.Popen(cmd, stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
