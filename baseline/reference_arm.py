@@ -47,14 +47,14 @@ def _ensure_copy() -> str | None:
 
 
 def run(args, model_cfg: dict, context: int, prefill_tokens: int, metric: str, peaks, clock_sampler) -> int:
+    import torch
+    if not torch.cuda.is_available():
+        return _unavailable("no CUDA device here: the reference's language path needs a GPU (flash-attn 2, Triton)")
     why = _ensure_copy()
     if why:
         return _unavailable(why)
     sys.path.insert(0, str(REF))
     try:
-        import torch
-        if not torch.cuda.is_available():
-            return _unavailable("no CUDA device here: the reference's language path needs a GPU (flash-attn 2, Triton)")
         from oxr_runtime.config import LanguageConfig
         from oxr_runtime.decode_graph import DecodeGraphs
         from oxr_runtime.kv_cache import BLOCK_SIZE, KVCache, blocks_for

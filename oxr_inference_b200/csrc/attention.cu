@@ -46,7 +46,19 @@ struct AttnArgs {
     float scale;
     int window;              // 0 = unlimited
     int* status;
+    // Extras of the cp.async tensor-core kernels (the other kernels leave them at their defaults):
+    int chunk = 0;                       // > 0: position p sees only keys of its own chunk, floor(p / chunk) == floor(j / chunk)
+    const float* dist_bias = nullptr;    // [bias_rows, H] fp32 added to the scaled score by distance p - j (last row: all larger ones)
+    int bias_rows = 0;
+    const float* sink = nullptr;         // [H] fp32: exp(sink) joins the softmax denominator (no key, no value, not scaled)
 };
+
+// First key that a query at position `pos` sees: the start of its window and of its chunk, whichever is later.
+__device__ __forceinline__ int key_lo(const AttnArgs& a, int pos) {
+    int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    if (a.chunk > 0) lo = max(lo, pos / a.chunk * a.chunk);
+    return lo;
+}
 
 template <typename T> struct Vec;   // 16-byte vectors of T
 template <> struct Vec<float> {
@@ -333,11 +345,13 @@ __device__ __forceinline__ const bf16* kv_elem(const bf16* base, int row, int d)
 
 // One warp: S = Q K^T for its 16 rows and NK keys starting at Kw, masked online softmax, O += P V.
 // qf: Q fragments when Q_IN_REGS, else read from Qw (this warp's 16 rows in shared memory).
+// row_lo: the first key each row sees (window, chunk); row_bias: null, or the row's column of a bias-by-distance table
+// [bias_rows, bias_stride] that is added (in natural-log units) to the scaled score.
 template <int NK, bool SWZ = false, bool QREG = Q_IN_REGS>
-__device__ __forceinline__ void warp_block(const uint32_t (&qf)[QREG ? KSTEPS : 1][4], const bf16* Qw, const bf16* Kw,
-                                           const bf16* Vw, int key0, const int (&row_pos)[2], const bool (&row_ok)[2],
-                                           int window, bool full_block, float scale_log2, float (&m)[2], float (&l)[2],
-                                           float (&o)[DT8][4]) {
+__device__ __forceinline__ void warp_block_ex(const uint32_t (&qf)[QREG ? KSTEPS : 1][4], const bf16* Qw, const bf16* Kw,
+                                              const bf16* Vw, int key0, const int (&row_pos)[2], const bool (&row_ok)[2],
+                                              const int (&row_lo)[2], const float* const (&row_bias)[2], int bias_rows, int bias_stride,
+                                              bool full_block, float scale_log2, float (&m)[2], float (&l)[2], float (&o)[DT8][4]) {
     constexpr int NT = NK / 8;
     const int lane = threadIdx.x & 31, t = lane & 3;
     float s[NT][4];
@@ -377,8 +391,10 @@ __device__ __forceinline__ void warp_block(const uint32_t (&qf)[QREG ? KSTEPS : 
             for (int e = 0; e < 4; ++e) {
                 const int r = e >> 1;
                 const int kp = key0 + i * 8 + 2 * t + (e & 1);
-                const bool seen = row_ok[r] && kp <= row_pos[r] && (window <= 0 || kp > row_pos[r] - window);
-                s[i][e] = seen ? s[i][e] * scale_log2 : -INFINITY;
+                const bool seen = row_ok[r] && kp <= row_pos[r] && kp >= row_lo[r];
+                float v = s[i][e] * scale_log2;
+                if (seen && row_bias[r] != nullptr) v = fmaf(row_bias[r][(size_t)min(row_pos[r] - kp, bias_rows - 1) * bias_stride], LOG2E, v);
+                s[i][e] = seen ? v : -INFINITY;
                 mx[r] = fmaxf(mx[r], s[i][e]);
             }
     }
@@ -427,6 +443,28 @@ __device__ __forceinline__ void warp_block(const uint32_t (&qf)[QREG ? KSTEPS : 
             mma16816(o[2 * dp + 1], ap, bv[2], bv[3]);
         }
     }
+}
+
+// The same with a window as the only lower bound and no bias.
+template <int NK, bool SWZ = false, bool QREG = Q_IN_REGS>
+__device__ __forceinline__ void warp_block(const uint32_t (&qf)[QREG ? KSTEPS : 1][4], const bf16* Qw, const bf16* Kw,
+                                           const bf16* Vw, int key0, const int (&row_pos)[2], const bool (&row_ok)[2],
+                                           int window, bool full_block, float scale_log2, float (&m)[2], float (&l)[2],
+                                           float (&o)[DT8][4]) {
+    const int row_lo[2] = {window > 0 ? row_pos[0] - window + 1 : 0, window > 0 ? row_pos[1] - window + 1 : 0};
+    const float* const no_bias[2] = {nullptr, nullptr};
+    warp_block_ex<NK, SWZ, QREG>(qf, Qw, Kw, Vw, key0, row_pos, row_ok, row_lo, no_bias, 0, 0, full_block, scale_log2, m, l, o);
+}
+
+// The sink's share of a finished row: (M, L, O) in log2 units become those of the softmax whose denominator also holds
+// exp(sink). Returns the factor for O; M and L are updated.
+__device__ __forceinline__ float add_sink(float sink, float& M, float& L) {
+    const float ms = sink * LOG2E;
+    const float top = fmaxf(M, ms);
+    const float keep = (M == -INFINITY) ? 0.f : exp2f(M - top);
+    L = L * keep + exp2f(ms - top);
+    M = top;
+    return keep;
 }
 
 // Row r of a tile of `rows` rows -> (token offset inside the request's new tokens, q head inside the group).
@@ -491,7 +529,7 @@ attn_mma_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     const int* table_row = a.block_table + (size_t)g.req * a.table_width;
 
     const int k_end = g.pos0 + g.tok_end;
-    const int k_lo = a.window > 0 ? max(0, g.pos0 + g.tok0 - a.window + 1) : 0;
+    const int k_lo = key_lo(a, g.pos0 + g.tok0);
     const int k_first = (k_lo / MMA_BN) * MMA_BN;
     const int n_blocks = (k_end - k_first + MMA_BN - 1) / MMA_BN;
 
@@ -499,13 +537,17 @@ attn_mma_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     load_kv_block(Ks, Vs, k_cache, v_cache, table_row, a, g.kvh, k_first, k_lo, k_end, g.req);
     cp_async_commit();
 
-    int row_pos[2];
+    int row_pos[2], row_head[2], row_lo[2];
     bool row_ok[2];
+    const float* row_bias[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
         int tok, gh;
         row_ok[r] = g.row(warp * 16 + (lane >> 2) + 8 * r, tok, gh);
         row_pos[r] = g.pos0 + tok;
+        row_head[r] = g.kvh * g.G + gh;
+        row_lo[r] = key_lo(a, row_pos[r]);
+        row_bias[r] = (a.dist_bias != nullptr && row_ok[r]) ? a.dist_bias + row_head[r] : nullptr;
     }
     float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
     float o[DT8][4];
@@ -548,10 +590,10 @@ attn_mma_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
         if (key0 <= warp_last_pos) {
             // every row of the warp holds a (token, head), the block ends at or before the earliest row's position and
             // starts inside the latest row's window
-            const bool full_block = warp_all_rows && key0 + MMA_BN - 1 <= warp_first_pos &&
-                                    (a.window <= 0 || key0 > warp_last_pos - a.window);
-            warp_block<MMA_BN>(qf, Qw, Ks + stage * MMA_BN * LDS, Vs + stage * MMA_BN * LDS, key0, row_pos, row_ok, a.window,
-                               full_block, scale_log2, m, l, o);
+            const bool full_block = warp_all_rows && key0 + MMA_BN - 1 <= warp_first_pos && key0 >= key_lo(a, warp_last_pos) &&
+                                    a.dist_bias == nullptr;
+            warp_block_ex<MMA_BN>(qf, Qw, Ks + stage * MMA_BN * LDS, Vs + stage * MMA_BN * LDS, key0, row_pos, row_ok, row_lo, row_bias,
+                                  a.bias_rows, a.H, full_block, scale_log2, m, l, o);
         }
         __syncthreads();   // everyone is done with this stage before the next prefetch overwrites it
     }
@@ -565,7 +607,9 @@ attn_mma_prefill_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, cons
     for (int r = 0; r < 2; ++r) {
         int tok, gh;
         if (!g.row(warp * 16 + (lane >> 2) + 8 * r, tok, gh)) continue;
-        const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+        float keep = 1.f;
+        if (a.sink != nullptr) keep = add_sink(a.sink[row_head[r]], m[r], l[r]);
+        const float inv = (l[r] > 0.f ? 1.f / l[r] : 0.f) * keep;
         bf16* dst = out + ((size_t)(g.q_begin + tok) * a.H + (size_t)g.kvh * g.G + gh) * D + 2 * (lane & 3);
 #pragma unroll
         for (int i = 0; i < DT8; ++i)
@@ -606,6 +650,10 @@ __device__ __forceinline__ void merge_warps(const float* mo, int nrows, int spli
             O.x += v.x * f; O.y += v.y * f; O.z += v.z * f; O.w += v.w * f;
         }
         if (splits == 1) {
+            if (a.sink != nullptr) {
+                const float keep = add_sink(a.sink[g.kvh * g.G + gh], M, L);
+                O.x *= keep; O.y *= keep; O.z *= keep; O.w *= keep;
+            }
             const float inv = L > 0.f ? 1.f / L : 0.f;
             uint2 packed;
             packed.x = pack_bf16(O.x * inv, O.y * inv);
@@ -659,6 +707,10 @@ __device__ __forceinline__ void merge_pieces(bf16* __restrict__ out, const float
             }
             M = m_new;
         }
+        if (a.sink != nullptr) {
+            const float keep = add_sink(a.sink[g.kvh * g.G + gh], M, L);
+            O.x *= keep; O.y *= keep; O.z *= keep; O.w *= keep;
+        }
         const float inv = L > 0.f ? 1.f / L : 0.f;
         uint2 packed;
         packed.x = pack_bf16(O.x * inv, O.y * inv);
@@ -694,7 +746,7 @@ attn_mma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
     int first = 0, count = 0, k_lo = 0, k_end = 0, k_first = 0;
     if (rows_live > 0) {
         k_end = g.pos0 + g.tok_end;
-        k_lo = a.window > 0 ? max(0, g.pos0 + g.tok0 - a.window + 1) : 0;
+        k_lo = key_lo(a, g.pos0 + g.tok0);
         k_first = (k_lo / MMA_BN) * MMA_BN;
         const int n_blocks = (k_end - k_first + MMA_BN - 1) / MMA_BN;
         const int per = (n_blocks + splits - 1) / splits;
@@ -713,13 +765,16 @@ attn_mma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
                               k_first + (first + st) * MMA_BN, k_lo, k_end, g.req);
             cp_async_commit();
         }
-        int row_pos[2];
+        int row_pos[2], row_lo[2];
         bool row_ok[2];
+        const float* row_bias[2];
 #pragma unroll
         for (int r = 0; r < 2; ++r) {
             int tok, gh;
             row_ok[r] = g.row((lane >> 2) + 8 * r, tok, gh);
             row_pos[r] = g.pos0 + tok;
+            row_lo[r] = key_lo(a, row_pos[r]);
+            row_bias[r] = (a.dist_bias != nullptr && row_ok[r]) ? a.dist_bias + (g.kvh * g.G + gh) : nullptr;
         }
         float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
         float o[DT8][4];
@@ -750,9 +805,9 @@ attn_mma_decode_kernel(bf16* __restrict__ out, float* __restrict__ part_o, float
             const int key0 = k_first + (first + b) * MMA_BN + warp * 16;   // this warp's quarter of the block
             // rows without a (token, head) have zero queries: unmasked they give finite numbers that are never stored,
             // so the block counts as fully visible when the rows that do exist see all of it
-            const bool full_block = key0 + 15 <= tile_first_pos && key0 >= k_lo && (a.window <= 0 || key0 > tile_last_pos - a.window);
-            warp_block<16>(qf, Qs, Ks + (stage * MMA_BN + warp * 16) * LDS, Vs + (stage * MMA_BN + warp * 16) * LDS, key0, row_pos,
-                           row_ok, a.window, full_block, scale_log2, m, l, o);
+            const bool full_block = key0 + 15 <= tile_first_pos && key0 >= key_lo(a, tile_last_pos) && a.dist_bias == nullptr;
+            warp_block_ex<16>(qf, Qs, Ks + (stage * MMA_BN + warp * 16) * LDS, Vs + (stage * MMA_BN + warp * 16) * LDS, key0, row_pos,
+                              row_ok, row_lo, row_bias, a.bias_rows, a.H, full_block, scale_log2, m, l, o);
             __syncthreads();
         }
 #pragma unroll
@@ -2164,13 +2219,58 @@ OXR_API int oxr_attn_tile_rows(int kind) {
 // cut (split-KV with TMA gathers only): 0 every request in `splits` equal pieces; 1 all key blocks of the step dealt out
 // evenly to one round of blocks, for requests of very different lengths (the scratch must then have
 // oxr_attn_even_cut_slots(units) slots, also with splits == 1).
+struct MaskExtras {
+    int chunk = 0;
+    const float* dist_bias = nullptr;
+    int bias_rows = 0;
+    const float* sink = nullptr;
+};
+
+static int paged_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                const int* short_req, const int* short_tok0, int n_short, const int* long_req,
+                                const int* long_tok0, int n_long, const int* cu_q, const int* ctx_lens,
+                                const int* block_table, int table_width, int page_size, int num_pages, int H, int KV,
+                                float scale, int window, int splits, float* part_o, float* part_ml, int* counters,
+                                const void* kv_maps, int pool_row0, int long_rows, int q_tokens, int cut, int* status, cudaStream_t stream,
+                                const MaskExtras& extras);
+
 OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache,
                                      const int* short_req, const int* short_tok0, int n_short, const int* long_req,
                                      const int* long_tok0, int n_long, const int* cu_q, const int* ctx_lens,
                                      const int* block_table, int table_width, int page_size, int num_pages, int H, int KV,
                                      float scale, int window, int splits, float* part_o, float* part_ml, int* counters,
                                      const void* kv_maps, int pool_row0, int long_rows, int q_tokens, int cut, int* status, cudaStream_t stream) {
+    return paged_attention_bf16(out, q, k_cache, v_cache, short_req, short_tok0, n_short, long_req, long_tok0, n_long, cu_q, ctx_lens, block_table,
+                                table_width, page_size, num_pages, H, KV, scale, window, splits, part_o, part_ml, counters, kv_maps, pool_row0,
+                                long_rows, q_tokens, cut, status, stream, MaskExtras{});
+}
+
+// The same attention with the extras of AttnArgs: a chunk mask, a bias by distance and a sink (see there). These run on the
+// cp.async tensor-core kernels only: no kv_maps, long tiles of 64 rows, cut 0.
+OXR_API int oxr_paged_attention_masked_bf16(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                            const int* short_req, const int* short_tok0, int n_short, const int* long_req,
+                                            const int* long_tok0, int n_long, const int* cu_q, const int* ctx_lens,
+                                            const int* block_table, int table_width, int page_size, int num_pages, int H, int KV,
+                                            float scale, int window, int chunk, const float* dist_bias, int bias_rows, const float* sink,
+                                            int splits, float* part_o, float* part_ml, int* counters, int* status, cudaStream_t stream) {
+    if (chunk < 0 || (dist_bias != nullptr && bias_rows <= 0)) return OXR_BAD_ARGUMENT;
+    MaskExtras extras;
+    extras.chunk = chunk; extras.dist_bias = dist_bias; extras.bias_rows = bias_rows; extras.sink = sink;
+    return paged_attention_bf16(out, q, k_cache, v_cache, short_req, short_tok0, n_short, long_req, long_tok0, n_long, cu_q, ctx_lens, block_table,
+                                table_width, page_size, num_pages, H, KV, scale, window, splits, part_o, part_ml, counters, nullptr, 0,
+                                PREFILL_ROWS, 0, 0, status, stream, extras);
+}
+
+static int paged_attention_bf16(void* out, const void* q, const void* k_cache, const void* v_cache,
+                                const int* short_req, const int* short_tok0, int n_short, const int* long_req,
+                                const int* long_tok0, int n_long, const int* cu_q, const int* ctx_lens,
+                                const int* block_table, int table_width, int page_size, int num_pages, int H, int KV,
+                                float scale, int window, int splits, float* part_o, float* part_ml, int* counters,
+                                const void* kv_maps, int pool_row0, int long_rows, int q_tokens, int cut, int* status, cudaStream_t stream,
+                                const MaskExtras& extras) {
     if (n_short <= 0 && n_long <= 0) return 0;
+    const bool masked = extras.chunk > 0 || extras.dist_bias != nullptr || extras.sink != nullptr;
+    if (masked && (kv_maps != nullptr || cut != 0 || (n_long > 0 && long_rows != PREFILL_ROWS))) return OXR_BAD_ARGUMENT;
     if (H <= 0 || KV <= 0 || H % KV != 0 || page_size <= 0 || table_width <= 0 || window < 0 || splits < 1) return OXR_BAD_ARGUMENT;
     if ((splits > 1 || cut != 0) && n_short > 0 && (part_o == nullptr || part_ml == nullptr || counters == nullptr)) return OXR_BAD_ARGUMENT;
     static bool configured = false;
@@ -2189,6 +2289,7 @@ OXR_API int oxr_paged_attention_bf16(void* out, const void* q, const void* k_cac
     for (int sh = 0; sh < 30; ++sh) if ((1 << sh) == page_size) a.page_shift = sh;
     a.heads_per_tile = a.tokens_per_tile = a.head_groups = 0;   // the tensor-core kernels derive these from their row count
     a.scale = scale; a.window = window; a.status = status;
+    a.chunk = extras.chunk; a.dist_bias = extras.dist_bias; a.bias_rows = extras.bias_rows; a.sink = extras.sink;
     if (n_long > 0 && long_rows == BIG_ROWS) {
         // long tiles of 256 rows: the tcgen05 kernel (the host made the tile list for 256 rows)
         if (!TMA_OK || D > 128 || kv_maps == nullptr || a.page_shift < 3 || !(scale > 0.f)) return OXR_BAD_ARGUMENT;

@@ -164,6 +164,8 @@ def _attn_lib(head_dim: int):
         lib.oxr_paged_attention.argtypes = [p, p, p, p, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p]
         lib.oxr_paged_attention.restype = c_int
         lib.oxr_paged_attention_bf16.argtypes = [p, p, p, p, p, p, i, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p, p, p, i, i, i, i, p, p]
+        lib.oxr_paged_attention_masked_bf16.argtypes = [p, p, p, p, p, p, i, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, i, p, i, p, p, p, p, p]
+        lib.oxr_paged_attention_masked_bf16.restype = c_int
         lib.oxr_attn_make_kv_maps.argtypes = [p, p, p, ctypes.c_ulonglong, i, i]
         lib.oxr_attn_make_kv_maps.restype = c_int
         lib.oxr_paged_attention_fused_decode_bf16.argtypes = [p, p, p, p, p, p, i, p, p, p, i, i, i, i, i, f, i, i, p, p, p, p, i, i, p, p, p, p, f, i, i,
@@ -481,10 +483,17 @@ def make_kv_maps(k_pool: torch.Tensor, v_pool: torch.Tensor, page_size: int) -> 
     return KVMaps(raw, address, (k_pool.data_ptr(), v_pool.data_ptr()), pages * page)
 
 
+def tiled_attention_takes(head_dim: int, value_dim: int, dtype: torch.dtype) -> bool:
+    """Whether the tiled tensor-core attention (``paged_attention``; one library per head size) serves these sizes: bfloat16, keys and
+    values of one size that is a multiple of 16 up to 256. Other sizes, and float32, go to ``attention_rows``."""
+    return dtype == torch.bfloat16 and head_dim == value_dim and head_dim % 16 == 0 and 16 <= head_dim <= 256
+
+
 def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, *, tiles: dict, cu_q: torch.Tensor,
                     ctx_lens: torch.Tensor, block_table: torch.Tensor, page_size: int, scale: float, window: int,
                     kv_len_bound: int, status: torch.Tensor, generic: bool = False, kv_maps: KVMaps | None = None,
-                    layer_in_pool: int = 0, uneven: bool = False) -> torch.Tensor:
+                    layer_in_pool: int = 0, uneven: bool = False, chunk: int = 0, dist_bias: torch.Tensor | None = None,
+                    sink: torch.Tensor | None = None) -> torch.Tensor:
     """Causal grouped-query attention of the step's new tokens over the paged cache
     (oxr_runtime/attention.py:47-109). ``q`` is ``[tokens, H, D]``; ``k_cache`` / ``v_cache`` are one layer's pool
     ``[pages, page_size, KV, D]``; ``window`` > 0 limits a query to its last ``window`` keys; ``tiles`` maps each
@@ -492,10 +501,18 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     the context lengths. float32 runs the fp32 CUDA-core kernel, bfloat16 the tensor-core kernels (``generic``
     forces the CUDA-core kernel, which then needs the float32 tile spec). With ``kv_maps`` (of the pool that
     ``k_cache`` / ``v_cache`` are layer ``layer_in_pool`` of) the split-KV kernel fetches K and V by TMA. ``uneven``: the
-    caller knows that the requests' lengths differ much (see ``DECODE_CUT``)."""
+    caller knows that the requests' lengths differ much (see ``DECODE_CUT``).
+
+    bfloat16 only, on the cp.async tensor-core kernels (no ``kv_maps``): ``chunk`` > 0 lets position p see only keys j with
+    ``j // chunk == p // chunk``; ``dist_bias [rows, H]`` (fp32) is added to the scaled score by distance p - j (the last row for all
+    larger ones); ``sink [H]`` (fp32) adds ``exp(sink)`` to the softmax denominator. ``v_cache`` may be ``k_cache`` itself (a latent
+    cache whose rows are key and value at once)."""
     _need(q, "q")
     _need(k_cache, "k_cache", q.dtype)
     _need(v_cache, "v_cache", q.dtype)
+    masked = chunk > 0 or dist_bias is not None or sink is not None
+    if masked and (q.dtype != torch.bfloat16 or generic or kv_maps is not None):
+        raise KernelError("paged_attention: chunk, dist_bias and sink run on the bfloat16 cp.async kernels only (no kv_maps)")
     for t, nm in ((cu_q, "cu_q"), (ctx_lens, "ctx_lens"), (block_table, "block_table")):
         _need(t, nm, torch.int32)
     _, num_heads, head_dim = q.shape
@@ -521,13 +538,28 @@ def paged_attention(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tenso
     l_req, l_tok, n_long = tiles[long_]
     splits, cut, part_o, part_ml, counters = _split_kv_plan(lib, n_short, num_heads, num_kv_heads, head_dim, kv_len_bound, kv_maps is not None,
                                                             uneven, q.device)
+    if masked:
+        for t, nm in ((dist_bias, "dist_bias"), (sink, "sink")):
+            if t is not None:
+                _need(t, nm, torch.float32)
+        if dist_bias is not None and (dist_bias.dim() != 2 or dist_bias.shape[1] != num_heads):
+            raise KernelError("paged_attention: the distance bias must be [rows, heads]")
+        if sink is not None and sink.numel() != num_heads:
+            raise KernelError("paged_attention: one sink per head")
+        code = lib.oxr_paged_attention_masked_bf16(out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), s_req.data_ptr(),
+                                                   s_tok.data_ptr(), n_short, l_req.data_ptr(), l_tok.data_ptr(), n_long, *common, int(chunk),
+                                                   _ptr(dist_bias), dist_bias.shape[0] if dist_bias is not None else 0, _ptr(sink), splits,
+                                                   _ptr(part_o), _ptr(part_ml), _ptr(counters), status.data_ptr(), _stream())
+        global launch_count
+        _done(code, "paged_attention_masked_bf16")
+        launch_count += 1 if n_long and n_short else 0
+        return out
     code = lib.oxr_paged_attention_bf16(out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), s_req.data_ptr(),
                                         s_tok.data_ptr(), n_short, l_req.data_ptr(), l_tok.data_ptr(), n_long, *common, splits,
                                         _ptr(part_o), _ptr(part_ml), _ptr(counters),
                                         kv_maps.address if kv_maps is not None else None,
                                         layer_in_pool * kv_maps.rows_per_layer if kv_maps is not None else 0, long_rows, q.shape[0], cut,
                                         status.data_ptr(), _stream())
-    global launch_count
     _done(code, "paged_attention_bf16")
     launch_count += 1 if n_long and n_short else 0
     return out

@@ -81,6 +81,16 @@ class MaskedAttention(Mixer):
     def cache_need(self) -> PagedKVNeed:
         return PagedKVNeed(self.KV, self.DK, self.window, value_dim=self.DV, chunk=self.chunk)
 
+    @property
+    def tiled(self) -> bool:
+        return ops.tiled_attention_takes(self.DK, self.DV, self.runtime.dtype)
+
+    def kernel_head_dims(self) -> tuple[int, ...]:
+        return (self.DK,) if self.tiled else ()
+
+    def tile_specs(self) -> list[tuple[int, int, int]]:
+        return ops.attention_tile_specs(self.H, self.KV, self.DK, self.runtime.dtype) if self.tiled else []
+
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         group = cache.group
         k_pool, v_pool = group.k_pool[cache.layer_in_group], group.v_pool[cache.layer_in_group]
@@ -91,6 +101,13 @@ class MaskedAttention(Mixer):
             q_cols, k_cols = self.H * self.DK, self.KV * self.DK
             ops.scatter_rows(k_pool, qkv, q_cols, k_cols, group.slots, ctx.status)
             ops.scatter_rows(v_pool, qkv, q_cols + k_cols, self.KV * self.DV, group.slots, ctx.status)
+        if self.tiled and qkv.dtype == torch.bfloat16:
+            # keys and values of one size the tiled kernels are built for: tensor cores, split-KV for single tokens
+            q = qkv[:, :self.H * self.DK].contiguous().view(ctx.n_tokens, self.H, self.DK)
+            o = ops.paged_attention(q, k_pool, v_pool, tiles=ctx.tiles, cu_q=ctx.cu_q, ctx_lens=ctx.ctx_lens, block_table=group.block_table,
+                                    page_size=group.page_size, scale=self.scale, window=self.window, kv_len_bound=ctx.kv_len_bound,
+                                    status=ctx.status, chunk=self.chunk, dist_bias=self.dist_bias)
+            return self.out(o.view(ctx.n_tokens, self.H * self.DV))
         o = ops.attention_rows(qkv, self.H, k_pool, v_pool, value_dim=self.DV, positions=ctx.positions, req_of_token=ctx.req_of_token,
                                block_table=group.block_table, scale=self.scale, chunk=self.chunk, window=self.window,
                                dist_bias=self.dist_bias, status=ctx.status)
@@ -151,6 +168,18 @@ class LatentAttention(Mixer):
     def cache_need(self) -> PagedKVNeed:
         return PagedKVNeed(1, self.L + self.R, 0, value_dim=0)
 
+    @property
+    def tiled(self) -> bool:
+        """The tiled kernels take the cached row as key and as value (both ``rank + rot_dim`` wide; the output's last ``rot_dim`` entries
+        are dropped), when that width is one of theirs."""
+        return ops.tiled_attention_takes(self.L + self.R, self.L + self.R, self.runtime.dtype)
+
+    def kernel_head_dims(self) -> tuple[int, ...]:
+        return (self.L + self.R,) if self.tiled else ()
+
+    def tile_specs(self) -> list[tuple[int, int, int]]:
+        return ops.attention_tile_specs(self.H, 1, self.L + self.R, self.runtime.dtype) if self.tiled else []
+
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         group = cache.group
         pool = group.k_pool[cache.layer_in_group]
@@ -166,8 +195,14 @@ class LatentAttention(Mixer):
         ops.latent_prep(pool, down, L, R, self.c_norm, self.eps, q, H, D + R, D, q_abs, L + R, L, cos, sin,
                         group.slots if cache.store else ctx.no_store_slots, ctx.status)
         ops.head_linear(q_abs, 0, q, 0, self.uk)
-        o_lat = ops.attention_rows(q_abs.view(n, H * (L + R)), H, pool, None, value_dim=L, positions=ctx.positions, req_of_token=ctx.req_of_token,
-                                   block_table=group.block_table, scale=self.scale, sink=self.sink, status=ctx.status)
+        if self.tiled and pool.dtype == torch.bfloat16:
+            o_lat = ops.paged_attention(q_abs, pool, pool, tiles=ctx.tiles, cu_q=ctx.cu_q, ctx_lens=ctx.ctx_lens, block_table=group.block_table,
+                                        page_size=group.page_size, scale=self.scale, window=0, kv_len_bound=ctx.kv_len_bound, status=ctx.status,
+                                        sink=self.sink)                       # [n, H, L + R]: the first L entries are the latent output
+        else:
+            o_lat = ops.attention_rows(q_abs.view(n, H * (L + R)), H, pool, None, value_dim=L, positions=ctx.positions,
+                                       req_of_token=ctx.req_of_token, block_table=group.block_table, scale=self.scale, sink=self.sink,
+                                       status=ctx.status).view(n, H, L)
         o = torch.empty((n, H, self.DV), dtype=pool.dtype, device=pool.device)
-        ops.head_linear(o, 0, o_lat.view(n, H, L), 0, self.uv)
+        ops.head_linear(o, 0, o_lat, 0, self.uv)
         return self.out(o.view(n, H * self.DV))

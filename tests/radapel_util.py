@@ -39,7 +39,7 @@ def model_config(layers, width=48, vocab=131, eps=1e-5, scale=0.7, loop=None):
 MODEL_X = model_config([mamba_layer(), attention_layer(), latent_layer(rot_dims=4), attention_layer(kv_heads=4, chunk=0, bias_rows=6, bias_max=9.5)],
                        loop=(1, 3, 3))
 MODEL_Y = model_config([latent_layer(heads=3, dim=8, rot_dim=16, rot_dims=16, vdim=16, kv_rank=40, mlp=None),
-                        attention_layer(heads=6, kv_heads=2, dim=8, vdim=8, chunk=7, bias_max=0, mlp=(24, 0.5)),
+                        attention_layer(heads=6, kv_heads=2, dim=16, vdim=16, chunk=7, bias_max=0, mlp=(24, 0.5)),
                         mamba_layer(heads=6, vdim=16, state=40, groups=3, conv=2, norm_groups=3, mlp=(72, 2.0))], width=64, vocab=200, eps=1e-6, scale=1.3)
 MODEL_Z = model_config([attention_layer(heads=2, kv_heads=1, dim=32, vdim=16, chunk=33, bias_max=100, bias_rows=20),
                         mamba_layer(heads=2, vdim=4, state=70, groups=1, conv=4, norm_groups=1, mlp=(32, 1.0))], width=40, vocab=97, loop=(0, 2, 2))

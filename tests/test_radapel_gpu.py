@@ -57,7 +57,11 @@ SINGLE = {
     "chunked_biased": RU.model_config([RU.attention_layer(mlp=None)]),
     "chunk_smaller_than_page": RU.model_config([RU.attention_layer(heads=6, kv_heads=3, dim=8, vdim=40, chunk=5, bias_rows=4, bias_max=3.5, mlp=None)]),
     "causal_no_bias": RU.model_config([RU.attention_layer(chunk=0, bias_max=0, mlp=None)]),
+    "tiled_chunked_biased": RU.model_config([RU.attention_layer(dim=32, vdim=32, mlp=None)]),
+    "tiled_causal_biased_many_heads": RU.model_config([RU.attention_layer(heads=20, kv_heads=1, dim=16, vdim=16, chunk=0, scale=0.2, mlp=None)]),
+    "tiled_chunk_of_three": RU.model_config([RU.attention_layer(heads=2, kv_heads=2, dim=48, vdim=48, chunk=3, bias_max=0, mlp=None)]),
     "latent_sink": RU.model_config([RU.latent_layer(mlp=None)]),
+    "latent_not_tiled": RU.model_config([RU.latent_layer(kv_rank=20, mlp=None)]),
     "latent_part_rotated": RU.model_config([RU.latent_layer(heads=5, dim=24, rot_dim=12, rot_dims=6, vdim=20, kv_rank=36, mlp=None)], width=56),
     "mamba2": RU.model_config([RU.mamba_layer()]),
     "mamba2_one_group_wide_state": RU.model_config([RU.mamba_layer(heads=3, vdim=5, state=130, groups=1, conv=5, norm_groups=1)]),
@@ -294,6 +298,65 @@ def test_keys_seen_and_not_seen(case, dtype):
     # the marked keys decide the output: hiding the mask's edge by one would have changed it
     shifted = _plain_attention(q, keys, values, [max(0, p - 1) for p in queries], 0.5, chunk, window, bias, sink)
     assert (shifted - want).abs().max() > 0.1
+
+
+@pytest.mark.parametrize("case", ["chunk_bias", "sink", "window_chunk"])
+def test_keys_seen_and_not_seen_by_the_tiled_kernels(case):
+    """The same marked keys through the tensor-core kernels (bfloat16, keys and values of one size): a prompt's portion that crosses
+    chunk edges (long tiles), a short portion, and single tokens of several requests with split keys."""
+    from oxr_inference_b200 import ops
+
+    g = torch.Generator().manual_seed(7)
+    H, KV, D, P, ctx = 4, 2, 32, 8, 300
+    chunk, window, bias, sink = 0, 0, None, None
+    if case == "chunk_bias":
+        chunk, bias = 20, torch.randn(9, H, generator=g)
+    elif case == "sink":
+        sink = torch.tensor([9.0, -4.0, 2.0, 30.0])
+    else:
+        chunk, window = 64, 12
+    keys = torch.randn(ctx, KV, D, generator=g) * 0.3
+    values = torch.randn(ctx, KV, D, generator=g)
+    direction = torch.randn(D, generator=g)
+    direction /= direction.norm()
+    for j in (0, 19, 20, 39, 40, 59, 60, 63, 64, 127, 128, 200, 255, 256, 288):
+        keys[j] += 6 * direction
+    keys, values = keys.to(torch.bfloat16).float(), values.to(torch.bfloat16).float()
+    k_pool, v_pool, table = _paged(keys, values, P, torch.bfloat16)
+    status = ops.new_status(DEV)
+    specs = ops.attention_tile_specs(H, KV, D, torch.bfloat16)
+
+    def run(q_lens, ctx_lens):
+        n = sum(q_lens)
+        q = (torch.randn(n, H, D, generator=g) * 0.3 + 4 * direction).to(torch.bfloat16)
+        cu = [0]
+        for x in q_lens:
+            cu.append(cu[-1] + x)
+        tiles = {}
+        for spec in specs:
+            req, tok0 = [], []
+            for r, x in enumerate(q_lens):
+                if spec[1] <= x <= spec[2]:
+                    for t0 in range(0, x, spec[0]):
+                        req.append(r)
+                        tok0.append(t0)
+            tiles[spec] = (torch.tensor(req + [0], dtype=torch.int32, device=DEV), torch.tensor(tok0 + [0], dtype=torch.int32, device=DEV), len(req))
+        out = ops.paged_attention(q.to(DEV), k_pool, v_pool, tiles=tiles, cu_q=torch.tensor(cu, dtype=torch.int32, device=DEV),
+                                  ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=DEV), block_table=table.repeat(len(q_lens), 1).contiguous(),
+                                  page_size=P, scale=0.5, window=window, kv_len_bound=max(ctx_lens), status=status, chunk=chunk,
+                                  dist_bias=None if bias is None else bias.to(DEV), sink=None if sink is None else sink.to(DEV))
+        ops.check_status(status)
+        at = 0
+        for x, c in zip(q_lens, ctx_lens):
+            positions = list(range(c - x, c))
+            want = _plain_attention(q[at:at + x].float(), keys, values, positions, 0.5, chunk, window, bias, sink)
+            err = (out[at:at + x].float().cpu() - want).abs().max()
+            assert err <= 2e-2 * max(1.0, want.abs().max()), f"{case}: request of {x} new tokens ending at {c}: off by {err:.2e}"
+            at += x
+
+    run([90, 5, 70], [130, 63, 300])                 # portions: long tiles, a short one
+    run([1] * 9, [20, 21, 40, 41, 64, 65, 129, 257, 300])   # single tokens at and around the edges
+    run([1, 33, 2, 1], [289, 290, 61, 1])            # mixed
 
 
 # ------------------------------------------------------------------------------------------------ small kernels against their formulas
