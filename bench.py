@@ -188,6 +188,254 @@ def serving_workload(which: str) -> int:
     return 0
 
 
+def radapel_config(width: int, ff: int, heads: int, kv_heads: int, head_dim: int, layers: int, vocab: int) -> dict:
+    """A Radapel model of a real model's layer sizes: its three mixers in turn (Mamba-2, chunked attention with a distance bias twice,
+    latent attention), each with a dense feed-forward, at the width, feed-forward size and head sizes of the Qwen3 model beside it."""
+    ff_part = {"kind": "dense", "ff": ff, "limit": 7.0}
+    attention = {"type": "attention", "mlp": ff_part, "mixer": {
+        "heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "mask": {"size": 1024},
+        "bias_max": 512, "bias_rows": 32}}
+    latent = {"type": "latent_attention", "mlp": ff_part, "mixer": {
+        "heads": heads, "dim": head_dim, "rot_dim": 64, "rot": {"dims": 64, "base": 10000.0}, "vdim": head_dim, "kv_rank": 192,
+        "scale": (head_dim + 64) ** -0.5}}
+    mamba = {"type": "mamba2", "mlp": ff_part, "mixer": {
+        "heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}}
+    turn = [mamba, attention, attention, latent]
+    return {"architecture": "Radapel", "embedding": {"scale": 1.0}, "norm": {"eps": 1e-6}, "vocab": vocab, "width": width,
+            "layers": [turn[i % 4] for i in range(layers)]}
+
+
+def _flush_l2(buf) -> None:
+    buf.add_(1)   # 512 MB written: more than L2 holds
+
+
+def _time_ms(fn, reps: int = 9, warm: int = 3, flush=None) -> float:
+    import torch
+
+    for _ in range(warm):
+        fn()
+    times = []
+    for _ in range(reps):
+        if flush is not None:
+            _flush_l2(flush)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b))
+    return statistics.median(times)
+
+
+def design_throughput(cfg: dict, vocab: int, K: int, W: int, batch: int, context: int, prefill_tokens: int) -> dict:
+    """Prefill (one prompt in one step, device time) and decode (``batch`` requests at ``context`` tokens, K replays of the decode
+    step's CUDA graph) of one model with random weights, through the engine."""
+    import torch
+
+    from oxr_inference_b200 import ops
+    from oxr_inference_b200.config import EngineSettings
+    from oxr_inference_b200.engine.api import Engine
+    from oxr_inference_b200.engine.batch import StepEntry
+    from oxr_inference_b200.sampling import SamplingParams
+
+    page = 16
+    pages = batch * ((context + 2 * (K + W) + 64) // page + 2) + prefill_tokens // page + 64
+    engine = Engine(random_config=cfg, seed=0, settings=EngineSettings(
+        dtype="bfloat16", page_size=page, num_pages=pages, max_running=batch, max_step_tokens=8192, prefill_chunk=2048,
+        max_positions=context + 2 * (K + W) + 128, cuda_graphs=True))
+    gen = torch.Generator().manual_seed(0)
+    # ---- prefill
+    ids = torch.randint(0, vocab, (prefill_tokens,), generator=gen).tolist()
+
+    def prefill():
+        rc = engine.runner.cache.open("prefill")
+        assert engine.runner.cache.reserve(rc, prefill_tokens)
+        engine.runner.step([StepEntry(rc, ids, [prefill_tokens - 1])])
+        engine.runner.cache.close(rc)
+
+    before = ops.launch_count
+    prefill()
+    prefill_launches = ops.launch_count - before
+    prefill_ms = _time_ms(prefill, reps=5, warm=W)
+    engine.runner.check()
+    # ---- decode
+    for _ in range(batch):
+        engine.add_request(torch.randint(0, vocab, (context,), generator=gen).tolist(), SamplingParams(max_tokens=2 * (K + W) + 8, ignore_eos=True))
+    while engine.scheduler.waiting or any(r.pending > 1 for r in engine.scheduler.running):
+        engine.step()
+    plan = engine.scheduler.schedule()
+    assert plan.decode_only and len(plan.entries) == batch
+    entries = [StepEntry(p.request.cache, p.request.tokens[p.start:p.start + 1], [0], counter=len(p.request.output)) for p in plan.entries]
+    tokens, _ = engine.graphs.run(entries)
+    key = engine.graphs.last_key
+    graph = engine.graphs._graphs[key][0]
+    for _ in range(W):
+        graph.replay()
+    torch.cuda.synchronize()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for _ in range(K):
+        graph.replay()
+    end.record()
+    torch.cuda.synchronize()
+    ms = start.elapsed_time(end) / K
+    engine.runner.check()
+    weights = sum(t.numel() * t.element_size() for part in engine.runner.model.parts() for t in vars(part).values() if isinstance(t, torch.Tensor))
+    return {"prefill_tok_s": round(prefill_tokens / (prefill_ms * 1e-3), 1), "prefill_ms": round(prefill_ms, 3), "prefill_launches": prefill_launches,
+            "decode_tok_s": round(batch * 1000.0 / ms, 1), "decode_ms_per_step": round(ms, 4), "decode_launches_per_step": engine.graphs.kernels_per_replay[key]}
+
+
+def radapel_kernels(width: int, heads: int, kv_heads: int, head_dim: int, ff: int) -> list[dict]:
+    """Each kernel of the new mixers alone, at one model size, beside the like kernel of the Qwen3 path: device time (median, L2 flushed
+    between calls), the bytes or FLOPs it has to move or do, and the fraction of the measured peak."""
+    import torch
+
+    from oxr_inference_b200 import ops
+
+    dev = "cuda"
+    hbm_gbs, bf16_tflops, _ = peaks()
+    flush = torch.zeros(128 << 20, dtype=torch.float32, device=dev)
+    status = ops.new_status(dev)
+    bf = torch.bfloat16
+    rows = []
+
+    def put(name, like, ms, *, bytes_=None, flops=None):
+        row = {"kernel": name, "like": like, "us": round(ms * 1e3, 1)}
+        if bytes_ is not None:
+            row.update(gb_s=round(bytes_ / (ms * 1e-3) / 1e9, 1), frac=round(bytes_ / (ms * 1e-3) / 1e9 / hbm_gbs, 4), bound="hbm")
+        else:
+            row.update(tflop_s=round(flops / (ms * 1e-3) / 1e12, 2), frac=round(flops / (ms * 1e-3) / 1e12 / bf16_tflops, 4), bound="tensor")
+        rows.append(row)
+
+    P, T, B, CTX = 16, 2048, 8, 2048
+    H, KV, D = heads, kv_heads, head_dim
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def rand(*shape, dtype=bf, scale=1.0):
+        return (torch.randn(*shape, generator=g, device=dev) * scale).to(dtype)
+
+    # ---- attention: a prompt of T tokens (prefill) and B single tokens over CTX keys (decode)
+    n_pages = B * (CTX // P) + T // P + 8
+    k_pool, v_pool = rand(n_pages, P, KV, D), rand(n_pages, P, KV, D)
+    bias = rand(513, H, dtype=torch.float32)
+    sink = rand(H, dtype=torch.float32)
+
+    def tiles_for(specs, q_lens):
+        out = {}
+        for spec in specs:
+            req = [r for r, x in enumerate(q_lens) if spec[1] <= x <= spec[2] for _ in range(0, x, spec[0])]
+            tok0 = [t0 for r, x in enumerate(q_lens) if spec[1] <= x <= spec[2] for t0 in range(0, x, spec[0])]
+            out[spec] = (torch.tensor(req + [0], dtype=torch.int32, device=dev), torch.tensor(tok0 + [0], dtype=torch.int32, device=dev), len(req))
+        return out
+
+    def attention_case(name, like, q_lens, ctx_lens, kv_heads_, k, v, *, tma, **extras):
+        n = sum(q_lens)
+        q = rand(n, H, k.shape[-1])
+        width_ = max(ctx_lens) // P + 1
+        table = torch.stack([torch.arange(r * (CTX // P), r * (CTX // P) + width_, dtype=torch.int32) % n_pages for r in range(len(q_lens))]).to(dev).contiguous()
+        maps = ops.make_kv_maps(k.unsqueeze(0), v.unsqueeze(0), P) if tma else None
+        specs = ops.attention_tile_specs(H, kv_heads_, k.shape[-1], bf, P if tma else None)
+        cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=dev)
+        args = dict(tiles=tiles_for(specs, q_lens), cu_q=cu, ctx_lens=torch.tensor(ctx_lens, dtype=torch.int32, device=dev), block_table=table,
+                    page_size=P, scale=D ** -0.5, window=0, kv_len_bound=max(ctx_lens), status=status, kv_maps=maps, **extras)
+        ms = _time_ms(lambda: ops.paged_attention(q, k, v, **args), flush=flush)
+        chunk = extras.get("chunk", 0)
+        if q_lens[0] > 1:
+            seen = sum(min(p % chunk, p) + 1 if chunk else p + 1 for x, c in zip(q_lens, ctx_lens) for p in range(c - x, c))
+            put(name, like, ms, flops=2 * 2 * H * k.shape[-1] * seen)
+        else:
+            seen = sum(min((c - 1) % chunk, c - 1) + 1 if chunk else c for c in ctx_lens)
+            put(name, like, ms, bytes_=seen * kv_heads_ * (k.shape[-1] + (0 if v is k else v.shape[-1])) * 2)
+
+    attention_case("paged_attention prefill (tcgen05, TMA)", None, [T], [T], KV, k_pool, v_pool, tma=True)
+    attention_case("paged_attention prefill (cp.async mma)", None, [T], [T], KV, k_pool, v_pool, tma=False)
+    attention_case("masked prefill: chunk 1024 + distance bias", "paged_attention prefill (cp.async mma)", [T], [T], KV, k_pool, v_pool, tma=False,
+                   chunk=1024, dist_bias=bias)
+    latent_pool = rand(n_pages, P, 1, 256)
+    attention_case("latent prefill: 256-wide shared row + sink", "paged_attention prefill (cp.async mma)", [T], [T], 1, latent_pool, latent_pool,
+                   tma=False, sink=sink)
+    attention_case("paged_attention decode b8 (TMA split-KV)", None, [1] * B, [CTX] * B, KV, k_pool, v_pool, tma=True)
+    attention_case("paged_attention decode b8 (cp.async split-KV)", None, [1] * B, [CTX] * B, KV, k_pool, v_pool, tma=False)
+    attention_case("masked decode b8: chunk 1024 + distance bias", "paged_attention decode b8 (cp.async split-KV)", [1] * B, [CTX] * B, KV, k_pool,
+                   v_pool, tma=False, chunk=1024, dist_bias=bias)
+    attention_case("latent decode b8: 256-wide shared row + sink", "paged_attention decode b8 (cp.async split-KV)", [1] * B, [CTX] * B, 1, latent_pool,
+                   latent_pool, tma=False, sink=sink)
+
+    # ---- Mamba-2: heads of 64 values, 128 states, 8 groups
+    MH, MP, MN, MG, taps = 2 * width // 64, 64, 128, 8, 4
+    inner, channels = MH * MP, MH * MP + 2 * MG * MN
+    state = torch.zeros(B + 1, MH * MP * MN + channels * (taps - 1), dtype=torch.float32, device=dev)
+    vec = {k: rand(*shape, dtype=torch.float32, scale=0.1) for k, shape in
+           (("conv", (channels, taps)), ("conv.b", (channels,)), ("dt_bias", (MH,)), ("A_log", (MH,)), ("D", (MH,)), ("norm", (inner,)))}
+    for name, q_lens in (("prefill 2048", [T]), ("decode b8", [1] * B)):
+        n = sum(q_lens)
+        proj = rand(n, 2 * inner + 2 * MG * MN + MH, scale=0.5)
+        cu = torch.tensor([0] + list(torch.tensor(q_lens).cumsum(0)), dtype=torch.int32, device=dev)
+        req = torch.repeat_interleave(torch.arange(len(q_lens), dtype=torch.int32), torch.tensor(q_lens)).to(dev)
+        slots = torch.arange(len(q_lens), dtype=torch.int32, device=dev)
+        common = dict(cu_q=cu, state_slots=slots, n_requests=len(q_lens))
+        ms = _time_ms(lambda: ops.mamba_conv(proj, inner, channels, vec["conv"], vec["conv.b"], state[:, MH * MP * MN:], req_of_token=req, **common), flush=flush)
+        put(f"mamba_conv {name}", "qk_norm_rope_store", ms, bytes_=n * channels * 2 * 2 + len(q_lens) * channels * (taps - 1) * 8)
+        xbc = ops.mamba_conv(proj, inner, channels, vec["conv"], vec["conv.b"], state[:, MH * MP * MN:], req_of_token=req, **common)
+        ms = _time_ms(lambda: ops.mamba_scan(xbc, proj, inner + channels, heads=MH, vdim=MP, state=MN, groups=MG, dt_bias=vec["dt_bias"],
+                                             a_log=vec["A_log"], d_skip=vec["D"], ssm=state, **common), flush=flush)
+        put(f"mamba_scan {name}", "paged_attention (same step)", ms, bytes_=n * (channels * 2 + inner * 4) + len(q_lens) * MH * MP * MN * 8)
+        y = torch.randn(n, inner, device=dev)
+        ms = _time_ms(lambda: ops.gated_group_norm(y, proj, 0, vec["norm"], 8, 1e-6), flush=flush)
+        put(f"gated_group_norm {name}", "add_rms_norm", ms, bytes_=n * inner * (4 + 2 + 2))
+
+    # ---- the stream's norms and the feed-forward's activation, beside the Qwen3 path's
+    for n in (T, B):
+        x, res, w = rand(n, width), torch.randn(n, width, device=dev), torch.ones(width, device=dev)
+        ms = _time_ms(lambda: ops.add_rms_norm(x, res, w, 1e-6), flush=flush)
+        put(f"add_rms_norm {n} rows", None, ms, bytes_=n * width * (2 + 4 + 4 + 2))
+        ms = _time_ms(lambda: ops.norm_add_norm(res, x, w, 1e-6, w, 1e-6), flush=flush)
+        put(f"norm_add_norm {n} rows", f"add_rms_norm {n} rows", ms, bytes_=n * width * (2 + 4 + 4 + 2))
+        gu = rand(n, 2 * ff)
+        ms = _time_ms(lambda: ops.silu_mul(gu), flush=flush)
+        put(f"silu_mul {n} rows", None, ms, bytes_=n * ff * 6)
+        ms = _time_ms(lambda: ops.clamped_glu(gu, alpha=1.702, limit=7.0), flush=flush)
+        put(f"clamped_glu {n} rows", f"silu_mul {n} rows", ms, bytes_=n * ff * 6)
+    # ---- the latent mixer's per-head maps (queries into the latent space, latent output to values)
+    for n in (T, B):
+        q = rand(n, H, D + 64)
+        q_abs = torch.empty(n, H, 256, dtype=bf, device=dev)
+        uk = rand(H, D, 192, scale=0.05)
+        ms = _time_ms(lambda: ops.head_linear(q_abs, 0, q, 0, uk), flush=flush)
+        put(f"head_linear {n} rows", "linear (same FLOPs)", ms, flops=2 * n * H * D * 192)
+    ops.check_status(status)
+    return rows
+
+
+def radapel_workload(args) -> int:
+    """The new design beside the closest existing one at equal sizes: whole-model prefill and decode throughput at two sizes, and every
+    kernel of the new mixers against its roofline beside the like kernel of the Qwen3 path."""
+    import torch
+
+    sizes = [("2048 wide, 8 layers", dict(width=2048, ff=8192, heads=16, kv_heads=4, head_dim=128, layers=8, vocab=32768)),
+             ("4096 wide, 8 layers (Qwen3-8B layer sizes)", dict(width=4096, ff=12288, heads=32, kv_heads=8, head_dim=128, layers=8, vocab=32768))]
+    K, W = args.steps, max(args.warmup, 3)
+    sampler = ClockSampler()
+    sampler.start()
+    out = {"workload": "radapel", "dtype": "bf16", "data": "synthetic uniform token ids, random weights N(0, 0.02)", "steps": K, "warmup": W,
+           "batch": 8, "context": args.context, "prefill_tokens": PREFILL_TOKENS, "peaks": peaks()[2], "sizes": []}
+    for name, s in sizes:
+        qwen = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_size": s["width"], "intermediate_size": s["ff"],
+                "num_hidden_layers": s["layers"], "num_attention_heads": s["heads"], "num_key_value_heads": s["kv_heads"], "head_dim": s["head_dim"],
+                "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "vocab_size": s["vocab"], "tie_word_embeddings": False,
+                "max_position_embeddings": 8192}
+        row = {"size": name}
+        for design, cfg in (("qwen3", qwen), ("radapel", radapel_config(**s))):
+            row[design] = design_throughput(cfg, s["vocab"], K, W, 8, args.context, PREFILL_TOKENS)
+            torch.cuda.empty_cache()
+        out["sizes"].append(row)
+    last = sizes[-1][1]
+    out["kernels"] = radapel_kernels(last["width"], last["heads"], last["kv_heads"], last["head_dim"], last["ff"])
+    out["clocks"] = sampler.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -198,14 +446,17 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the further points (quick runs)")
     ap.add_argument("--skip-serving", action="store_true", help="leave the two serving workloads out of `points`")
     ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds when the decode steps are timed")
-    ap.add_argument("--workload", default="decode", choices=("decode", "continuous", "chunked"),
-                    help="decode: the headline line (default); continuous / chunked: the two serving workloads, one line each")
+    ap.add_argument("--workload", default="decode", choices=("decode", "continuous", "chunked", "radapel"),
+                    help="decode: the headline line (default); continuous / chunked: the two serving workloads, one line each; "
+                         "radapel: the Radapel design beside Qwen3 at equal sizes, whole models and kernel by kernel")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"this engine runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
     if args.impl == "reference":
         return reference_arm(args)
+    if args.workload == "radapel":
+        return radapel_workload(args)
     if args.workload != "decode":
         return serving_workload(args.workload)
     K, W = args.steps, max(args.warmup, 3)
