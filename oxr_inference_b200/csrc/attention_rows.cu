@@ -121,10 +121,11 @@ OXR_API int oxr_attention_rows(void* out, const void* q, int q_stride, const voi
 }
 
 // ---------------------------------------------------------------------------------------------- cache writers
-// pool[slots[t], 0:width] = src[t, col0 : col0 + width]; a slot of -1 skips the row.
+// pool[slots[t], 0:width] = src[t, col0 : col0 + width]; a slot of -1 skips the row. With a second pool (keys and values of one
+// token): pool2[slots[t], 0:width2] = src[t, col0 + width : col0 + width + width2] in the same launch.
 template <typename T>
 __global__ void scatter_rows_kernel(T* __restrict__ pool, long long slot_stride, long long pool_slots, const T* __restrict__ src, int src_stride, int col0,
-                                    int width, const int* __restrict__ slots, int* status) {
+                                    int width, const int* __restrict__ slots, int* status, T* __restrict__ pool2, long long slot_stride2, int width2) {
     const int t = blockIdx.x;
     const int slot = slots[t];
     if (slot < 0) return;
@@ -133,14 +134,20 @@ __global__ void scatter_rows_kernel(T* __restrict__ pool, long long slot_stride,
         return;
     }
     for (int i = threadIdx.x; i < width; i += blockDim.x) pool[(long long)slot * slot_stride + i] = src[(size_t)t * src_stride + col0 + i];
+    if (pool2 != nullptr)
+        for (int i = threadIdx.x; i < width2; i += blockDim.x) pool2[(long long)slot * slot_stride2 + i] = src[(size_t)t * src_stride + col0 + width + i];
 }
 
 OXR_API int oxr_scatter_rows(void* pool, long long slot_stride, long long pool_slots, const void* src, int src_stride, int col0, int width,
-                             const int* slots, int n_tokens, int dtype, int* status, cudaStream_t stream) {
+                             const int* slots, int n_tokens, int dtype, int* status, void* pool2, long long slot_stride2, int width2,
+                             cudaStream_t stream) {
     if (n_tokens <= 0 || width <= 0) return 0;
-    if (dtype == 0) scatter_rows_kernel<float><<<n_tokens, 128, 0, stream>>>((float*)pool, slot_stride, pool_slots, (const float*)src, src_stride, col0, width, slots, status);
-    else scatter_rows_kernel<__nv_bfloat16><<<n_tokens, 128, 0, stream>>>((__nv_bfloat16*)pool, slot_stride, pool_slots, (const __nv_bfloat16*)src, src_stride, col0,
-                                                                         width, slots, status);
+    if (dtype == 0)
+        scatter_rows_kernel<float><<<n_tokens, 128, 0, stream>>>((float*)pool, slot_stride, pool_slots, (const float*)src, src_stride, col0, width, slots, status,
+                                                                (float*)pool2, slot_stride2, width2);
+    else
+        scatter_rows_kernel<__nv_bfloat16><<<n_tokens, 128, 0, stream>>>((__nv_bfloat16*)pool, slot_stride, pool_slots, (const __nv_bfloat16*)src, src_stride, col0,
+                                                                        width, slots, status, (__nv_bfloat16*)pool2, slot_stride2, width2);
     return oxr_launch_status();
 }
 
@@ -237,10 +244,90 @@ __global__ void __launch_bounds__(128) head_linear_kernel(T* __restrict__ out, i
     }
 }
 
+// The same on the tensor cores (bf16, fp32 sums in k order per 16-wide step): a block takes 64 tokens of one head, a warp 16 of them;
+// x rows and the head's matrix, 64 output columns at a time, stand in shared memory. n_in a multiple of 16, n_out of 16.
+__device__ __forceinline__ void hl_ldsm_x4(uint32_t (&r)[4], const __nv_bfloat16* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void hl_ldsm_x4_trans(uint32_t (&r)[4], const __nv_bfloat16* p) {
+    const uint32_t a = (uint32_t)__cvta_generic_to_shared(p);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];" : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(a));
+}
+__device__ __forceinline__ void hl_mma16816(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int HL_BM = 64, HL_BN = 64;
+
+__global__ void __launch_bounds__(128) head_linear_mma_kernel(__nv_bfloat16* __restrict__ out, int out_head_stride, int out0,
+                                                              const __nv_bfloat16* __restrict__ x, int x_head_stride, int x0,
+                                                              const __nv_bfloat16* __restrict__ w, int n_in, int n_out, int heads, int n_tokens) {
+    extern __shared__ __align__(16) unsigned char hl_smem[];
+    const int lda = n_in + 8, ldb = HL_BN + 8;
+    __nv_bfloat16* As = reinterpret_cast<__nv_bfloat16*>(hl_smem);   // [64][n_in + 8]
+    __nv_bfloat16* Bs = As + HL_BM * lda;                            // [n_in][64 + 8]
+    const int h = blockIdx.y, t0 = blockIdx.x * HL_BM, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    for (int i = threadIdx.x; i < HL_BM * n_in; i += 128) {
+        const int m = i / n_in, k = i % n_in;
+        As[m * lda + k] = (t0 + m < n_tokens) ? x[((size_t)(t0 + m) * heads + h) * x_head_stride + x0 + k] : __float2bfloat16_rn(0.f);
+    }
+    const __nv_bfloat16* wh = w + (size_t)h * n_in * n_out;
+    for (int c0 = 0; c0 < n_out; c0 += HL_BN) {
+        const int cols = min(HL_BN, n_out - c0);
+        __syncthreads();   // As is in; the previous chunk's Bs is no longer read
+        for (int i = threadIdx.x; i < n_in * HL_BN; i += 128) {
+            const int k = i / HL_BN, c = i % HL_BN;
+            Bs[k * ldb + c] = c < cols ? wh[(size_t)k * n_out + c0 + c] : __float2bfloat16_rn(0.f);
+        }
+        __syncthreads();
+        float acc[HL_BN / 8][4];
+#pragma unroll
+        for (int i = 0; i < HL_BN / 8; ++i) acc[i][0] = acc[i][1] = acc[i][2] = acc[i][3] = 0.f;
+        for (int kk = 0; kk < n_in / 16; ++kk) {
+            uint32_t a[4];
+            hl_ldsm_x4(a, As + (warp * 16 + (lane & 15)) * lda + kk * 16 + 8 * (lane >> 4));
+#pragma unroll
+            for (int np = 0; np < HL_BN / 16; ++np) {
+                uint32_t b[4];
+                hl_ldsm_x4_trans(b, Bs + (kk * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * ldb + np * 16 + 8 * (lane >> 4));
+                hl_mma16816(acc[2 * np], a, b[0], b[1]);
+                hl_mma16816(acc[2 * np + 1], a, b[2], b[3]);
+            }
+        }
+#pragma unroll
+        for (int r = 0; r < 2; ++r) {
+            const int t = t0 + warp * 16 + (lane >> 2) + 8 * r;
+            if (t >= n_tokens) continue;
+            __nv_bfloat16* dst = out + ((size_t)t * heads + h) * out_head_stride + out0 + c0 + 2 * (lane & 3);
+#pragma unroll
+            for (int i = 0; i < HL_BN / 8; ++i)
+                if (i * 8 + 2 * (lane & 3) < cols) {
+                    dst[i * 8] = __float2bfloat16_rn(acc[i][2 * r]);
+                    dst[i * 8 + 1] = __float2bfloat16_rn(acc[i][2 * r + 1]);
+                }
+        }
+    }
+}
+
 OXR_API int oxr_head_linear(void* out, int out_head_stride, int out0, const void* x, int x_head_stride, int x0, const void* w, int n_in, int n_out,
                             int heads, int n_tokens, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (n_in <= 0 || n_out <= 0 || heads <= 0 || heads > 65535) return OXR_BAD_ARGUMENT;
+    const size_t mma_smem = ((size_t)HL_BM * (n_in + 8) + (size_t)n_in * (HL_BN + 8)) * sizeof(__nv_bfloat16);
+    if (dtype == 1 && n_tokens > 16 && n_in % 16 == 0 && n_out % 16 == 0 && mma_smem <= 200 * 1024) {
+        static size_t configured = 0;
+        if (mma_smem > 48 * 1024 && mma_smem > configured) {
+            cudaError_t e = cudaFuncSetAttribute(head_linear_mma_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)mma_smem);
+            if (e != cudaSuccess) return 1000 + (int)e;
+            configured = mma_smem;
+        }
+        dim3 grid((n_tokens + HL_BM - 1) / HL_BM, heads);
+        head_linear_mma_kernel<<<grid, 128, mma_smem, stream>>>((__nv_bfloat16*)out, out_head_stride, out0, (const __nv_bfloat16*)x, x_head_stride, x0,
+                                                               (const __nv_bfloat16*)w, n_in, n_out, heads, n_tokens);
+        return oxr_launch_status();
+    }
     constexpr int TM = 8;
     const size_t smem = (size_t)TM * n_in * sizeof(float);
     if (smem > 48 * 1024) return OXR_BAD_ARGUMENT;

@@ -2,15 +2,15 @@
 // with SiLU, the roll of the convolution's tail, the selective-state recurrence, and the gated grouped RMSNorm.
 //
 // A step brings, per request, any number of new tokens (a portion of a prompt, or one decoded token); what earlier steps
-// left is the per-request state in a slot: the recurrence's S [heads, vdim, N] and the last taps-1 inputs of the
+// left is the per-request state in a slot: the recurrence's S [heads, N, vdim] and the last taps-1 inputs of the
 // convolution [channels, taps-1], both fp32. Everything that enters the recurrence is fp32: dt = softplus(dt + bias)
 // (no clamp), the decay exp(-exp(A_log) dt), S itself and the sums over it. T is the activation type of the projections.
 //
 //   S_t = decay_t S_(t-1) + dt_t B_t x_t^T          y_t = S_t^T C_t + D x_t
 //
 // The recurrence runs token by token in the order of the sequence whatever the cut, so a position's result does not
-// depend on how the prompt was cut into steps. Columns of S (one value dimension p each) are independent: a warp owns
-// one column, its lanes the N state entries, and one block takes a few columns of one head of one request.
+// depend on how the prompt was cut into steps. Columns of S (one value dimension p each) are independent: a block takes
+// 32 columns of one head of one request.
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------------------- convolution
@@ -55,67 +55,90 @@ __global__ void conv_tail_roll_kernel(float* __restrict__ state, long long slot_
 // ---------------------------------------------------------------------------------------------- recurrence
 __device__ __forceinline__ float softplus_f32(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
 
-// grid (ceil(vdim / WARPS), heads, requests); warp w owns column p = blockIdx.x * WARPS + w; lane l holds S[p, l + 32 k].
-template <typename T, int NPL, int WARPS>
-__global__ void __launch_bounds__(32 * WARPS) ssm_scan_kernel(
+// grid (ceil(vdim / 32), heads, requests); block = 32 * NW threads with NW = ceil(N / 32). Lane l owns the value column
+// p = 32 blockIdx.x + l, warp w the state entries n = 32 w .. 32 w + 31, so a thread keeps 32 entries of S in registers and
+// updates them with plain multiply-adds: B and C of a token are the same for all lanes and come from shared memory as
+// broadcast 16-byte loads, no shuffles. The step's tokens go through shared memory TT at a time (B, C, x, softplus and decay,
+// each computed once per token and block); the warps' partial sums of y meet there too and are added in the order of the warps.
+// S is stored [heads, N, vdim]: the lanes of a warp read and write 128 contiguous bytes per state entry.
+template <typename T, int NW, int TT>
+__global__ void __launch_bounds__(32 * NW) ssm_scan_kernel(
     float* __restrict__ y, const T* __restrict__ xbc, const T* __restrict__ proj, int proj_stride, int dt_col0, int heads, int vdim, int N,
     int groups, const float* __restrict__ dt_bias, const float* __restrict__ a_log, const float* __restrict__ d_skip, float* __restrict__ state,
     long long slot_stride, const int* __restrict__ cu_q, const int* __restrict__ state_slots) {
+    constexpr int NP = 32 * NW;                       // N rounded up to whole warps
+    extern __shared__ __align__(16) float scan_smem[];
+    float* Bs = scan_smem;                            // [TT][NP]
+    float* Cs = Bs + TT * NP;                         // [TT][NP]
+    float* xs = Cs + TT * NP;                         // [TT][32]
+    float* part = xs + TT * 32;                       // [TT][NW][32]
+    float* dts = part + TT * NW * 32;                 // [TT]
+    float* decays = dts + TT;                         // [TT]
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int p = blockIdx.x * WARPS + warp, h = blockIdx.y, r = blockIdx.z;
-    if (p >= vdim) return;
+    const int p0 = blockIdx.x * 32, p = p0 + lane, h = blockIdx.y, r = blockIdx.z;
     const int t0 = cu_q[r], t1 = cu_q[r + 1];
     if (t1 <= t0) return;
     const int inner = heads * vdim, channels = inner + 2 * groups * N, g = h / (heads / groups);
-    float* S = state + (long long)state_slots[r] * slot_stride + ((long long)h * vdim + p) * N;
-    float s[NPL];
+    const int b_col = inner + g * N, c_col = inner + groups * N + g * N, n0 = 32 * warp;
+    float* S = state + (long long)state_slots[r] * slot_stride + (long long)h * N * vdim;
+    float s[32];
 #pragma unroll
-    for (int k = 0; k < NPL; ++k) s[k] = (lane + 32 * k < N) ? S[lane + 32 * k] : 0.f;
+    for (int k = 0; k < 32; ++k) s[k] = (n0 + k < N && p < vdim) ? S[(size_t)(n0 + k) * vdim + p] : 0.f;
     const float neg_a = -expf(a_log[h]), bias = dt_bias[h], skip = d_skip[h];
-    const int x_col = h * vdim + p, b_col = inner + g * N, c_col = inner + groups * N + g * N;
 
-    // the next token's inputs are fetched while this token's sums run
-    float dt_raw = Num<T>::to_f32(proj[(size_t)t0 * proj_stride + dt_col0 + h]);
-    float x = Num<T>::to_f32(xbc[(size_t)t0 * channels + x_col]);
-    float b[NPL], c[NPL];
+    for (int tile = t0; tile < t1; tile += TT) {
+        const int nt = min(TT, t1 - tile);
+        for (int i = threadIdx.x; i < nt * NP; i += 32 * NW) {
+            const int t = i / NP, n = i % NP;
+            const T* row = xbc + (size_t)(tile + t) * channels;
+            Bs[i] = n < N ? Num<T>::to_f32(row[b_col + n]) : 0.f;
+            Cs[i] = n < N ? Num<T>::to_f32(row[c_col + n]) : 0.f;
+        }
+        for (int i = threadIdx.x; i < nt * 32; i += 32 * NW) {
+            const int t = i >> 5, c = i & 31;
+            xs[i] = (p0 + c < vdim) ? Num<T>::to_f32(xbc[(size_t)(tile + t) * channels + h * vdim + p0 + c]) : 0.f;
+        }
+        if (threadIdx.x < nt) {
+            const float dt = softplus_f32(Num<T>::to_f32(proj[(size_t)(tile + threadIdx.x) * proj_stride + dt_col0 + h]) + bias);
+            dts[threadIdx.x] = dt;
+            decays[threadIdx.x] = expf(neg_a * dt);
+        }
+        __syncthreads();
+        for (int t = 0; t < nt; ++t) {
+            const float decay = decays[t], dx = dts[t] * xs[t * 32 + lane];
+            const float4* b4 = reinterpret_cast<const float4*>(Bs + t * NP + n0);
+            const float4* c4 = reinterpret_cast<const float4*>(Cs + t * NP + n0);
+            float sum = 0.f;
 #pragma unroll
-    for (int k = 0; k < NPL; ++k) {
-        const int n = lane + 32 * k;
-        b[k] = n < N ? Num<T>::to_f32(xbc[(size_t)t0 * channels + b_col + n]) : 0.f;
-        c[k] = n < N ? Num<T>::to_f32(xbc[(size_t)t0 * channels + c_col + n]) : 0.f;
-    }
-    for (int t = t0; t < t1; ++t) {
-        const float dt_now = dt_raw, x_now = x;
-        float b_now[NPL], c_now[NPL];
-#pragma unroll
-        for (int k = 0; k < NPL; ++k) { b_now[k] = b[k]; c_now[k] = c[k]; }
-        if (t + 1 < t1) {
-            dt_raw = Num<T>::to_f32(proj[(size_t)(t + 1) * proj_stride + dt_col0 + h]);
-            x = Num<T>::to_f32(xbc[(size_t)(t + 1) * channels + x_col]);
-#pragma unroll
-            for (int k = 0; k < NPL; ++k) {
-                const int n = lane + 32 * k;
-                if (n < N) {
-                    b[k] = Num<T>::to_f32(xbc[(size_t)(t + 1) * channels + b_col + n]);
-                    c[k] = Num<T>::to_f32(xbc[(size_t)(t + 1) * channels + c_col + n]);
-                }
+            for (int k4 = 0; k4 < 8; ++k4) {
+                const float4 b = b4[k4], c = c4[k4];
+                s[4 * k4] = fmaf(decay, s[4 * k4], dx * b.x);
+                sum = fmaf(s[4 * k4], c.x, sum);
+                s[4 * k4 + 1] = fmaf(decay, s[4 * k4 + 1], dx * b.y);
+                sum = fmaf(s[4 * k4 + 1], c.y, sum);
+                s[4 * k4 + 2] = fmaf(decay, s[4 * k4 + 2], dx * b.z);
+                sum = fmaf(s[4 * k4 + 2], c.z, sum);
+                s[4 * k4 + 3] = fmaf(decay, s[4 * k4 + 3], dx * b.w);
+                sum = fmaf(s[4 * k4 + 3], c.w, sum);
             }
+            part[(t * NW + warp) * 32 + lane] = sum;
         }
-        const float dt = softplus_f32(dt_now + bias);
-        const float decay = expf(neg_a * dt);
-        const float dx = dt * x_now;
-        float part = 0.f;
+        __syncthreads();
+        for (int i = threadIdx.x; i < nt * 32; i += 32 * NW) {
+            const int t = i >> 5, c = i & 31;
+            if (p0 + c >= vdim) continue;
+            float v = 0.f;
 #pragma unroll
-        for (int k = 0; k < NPL; ++k) {
-            s[k] = fmaf(decay, s[k], dx * b_now[k]);
-            part = fmaf(s[k], c_now[k], part);
+            for (int w = 0; w < NW; ++w) v += part[(t * NW + w) * 32 + c];
+            y[(size_t)(tile + t) * inner + h * vdim + p0 + c] = fmaf(skip, xs[i], v);
         }
-        part = warp_sum(part);
-        if (lane == 0) y[(size_t)t * inner + x_col] = fmaf(skip, x_now, part);
+        __syncthreads();   // the tile's buffers are free for the next one
     }
+    if (p < vdim) {
 #pragma unroll
-    for (int k = 0; k < NPL; ++k)
-        if (lane + 32 * k < N) S[lane + 32 * k] = s[k];
+        for (int k = 0; k < 32; ++k)
+            if (n0 + k < N) S[(size_t)(n0 + k) * vdim + p] = s[k];
+    }
 }
 
 // ---------------------------------------------------------------------------------------------- gated grouped norm
@@ -168,14 +191,16 @@ OXR_API int oxr_mamba_conv(void* out, const void* proj, int n_tokens, int n_requ
                                                   req_of_token, cu_q, state_slots, stream);
 }
 
-template <typename T, int NPL>
+template <typename T, int NW>
 static void mamba_scan(float* y, const void* xbc, const void* proj, int n_requests, int proj_stride, int dt_col0, int heads, int vdim, int N, int groups,
                        const float* dt_bias, const float* a_log, const float* d_skip, float* state, long long slot_stride, const int* cu_q,
                        const int* state_slots, cudaStream_t stream) {
-    constexpr int WARPS = 4;
-    dim3 grid((vdim + WARPS - 1) / WARPS, heads, n_requests);
-    ssm_scan_kernel<T, NPL, WARPS><<<grid, 32 * WARPS, 0, stream>>>(y, (const T*)xbc, (const T*)proj, proj_stride, dt_col0, heads, vdim, N, groups, dt_bias,
-                                                                    a_log, d_skip, state, slot_stride, cu_q, state_slots);
+    constexpr int TT = NW <= 4 ? 16 : 8;
+    constexpr size_t smem = (size_t)(TT * (2 * 32 * NW + 32 + NW * 32 + 2)) * sizeof(float);
+    static_assert(smem <= 48 * 1024, "the tile fits the default shared memory");
+    dim3 grid((vdim + 31) / 32, heads, n_requests);
+    ssm_scan_kernel<T, NW, TT><<<grid, 32 * NW, smem, stream>>>(y, (const T*)xbc, (const T*)proj, proj_stride, dt_col0, heads, vdim, N, groups, dt_bias,
+                                                                a_log, d_skip, state, slot_stride, cu_q, state_slots);
 }
 
 OXR_API int oxr_mamba_scan(float* y, const void* xbc, const void* proj, int n_requests, int proj_stride, int dt_col0, int heads, int vdim, int N, int groups,
@@ -183,16 +208,22 @@ OXR_API int oxr_mamba_scan(float* y, const void* xbc, const void* proj, int n_re
                            const int* state_slots, int dtype, cudaStream_t stream) {
     if (n_requests <= 0) return 0;
     if (heads <= 0 || vdim <= 0 || N <= 0 || N > 256 || groups <= 0 || heads % groups || n_requests > 65535 || heads > 65535) return OXR_BAD_ARGUMENT;
-    const int npl = (N + 31) / 32;
-#define OXR_SCAN(NPL) \
-    (dtype == 0 ? mamba_scan<float, NPL>(y, xbc, proj, n_requests, proj_stride, dt_col0, heads, vdim, N, groups, dt_bias, a_log, d_skip, state, \
-                                         slot_stride, cu_q, state_slots, stream) \
-                : mamba_scan<__nv_bfloat16, NPL>(y, xbc, proj, n_requests, proj_stride, dt_col0, heads, vdim, N, groups, dt_bias, a_log, d_skip, state, \
-                                                 slot_stride, cu_q, state_slots, stream))
-    if (npl <= 1) OXR_SCAN(1);
-    else if (npl <= 2) OXR_SCAN(2);
-    else if (npl <= 4) OXR_SCAN(4);
-    else OXR_SCAN(8);
+    const int nw = (N + 31) / 32;
+#define OXR_SCAN(NW) \
+    (dtype == 0 ? mamba_scan<float, NW>(y, xbc, proj, n_requests, proj_stride, dt_col0, heads, vdim, N, groups, dt_bias, a_log, d_skip, state, \
+                                        slot_stride, cu_q, state_slots, stream) \
+                : mamba_scan<__nv_bfloat16, NW>(y, xbc, proj, n_requests, proj_stride, dt_col0, heads, vdim, N, groups, dt_bias, a_log, d_skip, state, \
+                                                slot_stride, cu_q, state_slots, stream))
+    switch (nw) {
+        case 1: OXR_SCAN(1); break;
+        case 2: OXR_SCAN(2); break;
+        case 3: OXR_SCAN(3); break;
+        case 4: OXR_SCAN(4); break;
+        case 5: OXR_SCAN(5); break;
+        case 6: OXR_SCAN(6); break;
+        case 7: OXR_SCAN(7); break;
+        default: OXR_SCAN(8); break;
+    }
 #undef OXR_SCAN
     return oxr_launch_status();
 }

@@ -55,6 +55,79 @@ __global__ void norm_add_norm_kernel(float* __restrict__ stream, const T* __rest
     }
 }
 
+// The same for bf16 rows that are whole 16-byte words: a thread keeps its VPT words of y and of the stream in registers from the
+// first load to the last store, so every row is read once, with 16-byte loads.
+__device__ __forceinline__ void bf16x8_to_f32(const uint4& v, float (&out)[8]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+        const float2 f = __bfloat1622float2(h[i]);
+        out[2 * i] = f.x; out[2 * i + 1] = f.y;
+    }
+}
+__device__ __forceinline__ uint4 f32_to_bf16x8(const float (&v)[8]) {
+    uint4 out;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    return out;
+}
+
+template <int VPT>
+__global__ void norm_add_norm_bf16x8_kernel(float* __restrict__ stream, const __nv_bfloat16* __restrict__ y, const float* __restrict__ w_post,
+                                            __nv_bfloat16* __restrict__ out, const float* __restrict__ w_next, int hidden, float eps_post,
+                                            float eps_next) {
+    __shared__ float red[32];
+    const size_t at = (size_t)blockIdx.x * hidden;
+    const int nvec = hidden / 8;
+    float yv[VPT][8], sv[VPT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int idx = threadIdx.x + v * blockDim.x;
+        if (idx < nvec) {
+            bf16x8_to_f32(*reinterpret_cast<const uint4*>(y + at + 8 * idx), yv[v]);
+            const float4 a = *reinterpret_cast<const float4*>(stream + at + 8 * idx), b = *reinterpret_cast<const float4*>(stream + at + 8 * idx + 4);
+            sv[v][0] = a.x; sv[v][1] = a.y; sv[v][2] = a.z; sv[v][3] = a.w; sv[v][4] = b.x; sv[v][5] = b.y; sv[v][6] = b.z; sv[v][7] = b.w;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) ss = fmaf(yv[v][i], yv[v][i], ss);
+        }
+    }
+    ss = block_sum(ss, red);
+    const float inv = 1.f / sqrtf(ss / (float)hidden + eps_post);
+    float s2 = 0.f;
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int idx = threadIdx.x + v * blockDim.x;
+        if (idx < nvec) {
+            const float4 wa = *reinterpret_cast<const float4*>(w_post + 8 * idx), wb = *reinterpret_cast<const float4*>(w_post + 8 * idx + 4);
+            const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+                sv[v][i] += yv[v][i] * inv * w[i];
+                s2 = fmaf(sv[v][i], sv[v][i], s2);
+            }
+            *reinterpret_cast<float4*>(stream + at + 8 * idx) = make_float4(sv[v][0], sv[v][1], sv[v][2], sv[v][3]);
+            *reinterpret_cast<float4*>(stream + at + 8 * idx + 4) = make_float4(sv[v][4], sv[v][5], sv[v][6], sv[v][7]);
+        }
+    }
+    if (out == nullptr) return;
+    s2 = block_sum(s2, red);
+    const float inv2 = 1.f / sqrtf(s2 / (float)hidden + eps_next);
+#pragma unroll
+    for (int v = 0; v < VPT; ++v) {
+        const int idx = threadIdx.x + v * blockDim.x;
+        if (idx < nvec) {
+            const float4 wa = *reinterpret_cast<const float4*>(w_next + 8 * idx), wb = *reinterpret_cast<const float4*>(w_next + 8 * idx + 4);
+            const float w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+            float o[8];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) o[i] = sv[v][i] * inv2 * w[i];
+            *reinterpret_cast<uint4*>(out + at + 8 * idx) = f32_to_bf16x8(o);
+        }
+    }
+}
+
 // out[r] = [ a[r] | b[r] ] rounded to T
 template <typename T>
 __global__ void concat2_cast_kernel(T* __restrict__ out, const float* __restrict__ a, const float* __restrict__ b, int hidden, size_t total) {
@@ -92,6 +165,22 @@ __global__ void clamped_glu_kernel(T* __restrict__ out, const T* __restrict__ ga
     }
 }
 
+// bf16, [gate | up] side by side, `inter` a multiple of 8: 16-byte loads and stores. Grid (column words, rows).
+__global__ void clamped_glu_bf16x8_kernel(uint4* __restrict__ out, const uint4* __restrict__ gate_up, int inter8, float alpha, float limit) {
+    const int c = blockIdx.x * blockDim.x + threadIdx.x;
+    if (c >= inter8) return;
+    const size_t row = blockIdx.y;
+    float g[8], u[8], o[8];
+    bf16x8_to_f32(gate_up[row * 2 * inter8 + c], g);
+    bf16x8_to_f32(gate_up[row * 2 * inter8 + inter8 + c], u);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const float gg = fminf(g[i], limit), uu = fminf(fmaxf(u[i], -limit), limit);
+        o[i] = gg / (1.f + __expf(-alpha * gg)) * (uu + 1.f);
+    }
+    out[row * inter8 + c] = f32_to_bf16x8(o);
+}
+
 // ---------------------------------------------------------------------------------------------- rotary angles
 // cos/sin [tokens, half] of position * freq[i], the product and the functions in fp64, rounded once to fp32.
 __global__ void rotary_angles_kernel(float* __restrict__ cos_out, float* __restrict__ sin_out, const int* __restrict__ positions,
@@ -124,6 +213,18 @@ OXR_API int oxr_norm_add_norm(float* stream, const void* y, const float* w_post,
                               float eps_post, float eps_next, int dtype, cudaStream_t stream_) {
     if (n <= 0) return 0;
     if (hidden <= 0 || (out != nullptr && w_next == nullptr)) return OXR_BAD_ARGUMENT;
+    if (dtype == 1 && hidden % 8 == 0 && hidden <= 32768 && (uintptr_t)stream % 16 == 0 && (uintptr_t)y % 16 == 0 && (uintptr_t)out % 16 == 0 &&
+        (uintptr_t)w_post % 16 == 0 && (uintptr_t)w_next % 16 == 0) {
+        const int nvec = hidden / 8;
+        const int vpt = nvec <= 512 ? 1 : (nvec <= 2048 ? 2 : 4);
+        const int threads = ((nvec + vpt - 1) / vpt + 31) / 32 * 32;
+        const __nv_bfloat16* yb = (const __nv_bfloat16*)y;
+        __nv_bfloat16* ob = (__nv_bfloat16*)out;
+        if (vpt == 1) norm_add_norm_bf16x8_kernel<1><<<n, threads, 0, stream_>>>(stream, yb, w_post, ob, w_next, hidden, eps_post, eps_next);
+        else if (vpt == 2) norm_add_norm_bf16x8_kernel<2><<<n, threads, 0, stream_>>>(stream, yb, w_post, ob, w_next, hidden, eps_post, eps_next);
+        else norm_add_norm_bf16x8_kernel<4><<<n, threads, 0, stream_>>>(stream, yb, w_post, ob, w_next, hidden, eps_post, eps_next);
+        return oxr_launch_status();
+    }
     const int threads = hidden >= 1024 ? 256 : 128;
     const int keep = hidden <= 8192 ? hidden : 0;
     const size_t smem = (32 + keep) * sizeof(float);
@@ -154,6 +255,11 @@ OXR_API int oxr_clamped_glu(void* out, const void* gate_up, int n, int inter, in
                             cudaStream_t stream_) {
     if (n <= 0) return 0;
     if (inter <= 0 || interleave < 0 || (interleave && inter % interleave)) return OXR_BAD_ARGUMENT;
+    if (dtype == 1 && interleave == 0 && inter % 8 == 0 && n <= 65535 && (uintptr_t)out % 16 == 0 && (uintptr_t)gate_up % 16 == 0) {
+        dim3 grid((inter / 8 + 127) / 128, n);
+        clamped_glu_bf16x8_kernel<<<grid, 128, 0, stream_>>>((uint4*)out, (const uint4*)gate_up, inter / 8, alpha, limit);
+        return oxr_launch_status();
+    }
     const size_t total = (size_t)n * inter;
     if (dtype == 0) clamped_glu_kernel<float><<<grid_for(total, 256), 256, 0, stream_>>>((float*)out, (const float*)gate_up, inter, interleave, alpha, limit, total);
     else clamped_glu_kernel<__nv_bfloat16><<<grid_for(total, 256), 256, 0, stream_>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gate_up, inter, interleave,

@@ -135,7 +135,7 @@ def _lib():
         lib.oxr_mamba_scan.argtypes = [p, p, p, i, i, i, i, i, i, i, p, p, p, p, ll, p, p, i, p]
         lib.oxr_gated_group_norm.argtypes = [p, p, p, i, i, i, p, i, i, f, i, p]
         lib.oxr_attention_rows.argtypes = [p, p, i, p, ll, i, p, ll, i, i, i, i, i, i, p, p, p, i, i, i, f, i, i, p, i, p, i, p, p]
-        lib.oxr_scatter_rows.argtypes = [p, ll, ll, p, i, i, i, p, i, i, p, p]
+        lib.oxr_scatter_rows.argtypes = [p, ll, ll, p, i, i, i, p, i, i, p, p, ll, i, p]
         lib.oxr_latent_prep.argtypes = [p, ll, ll, p, i, i, p, f, p, i, i, i, p, i, i, p, p, i, p, i, i, p, p]
         lib.oxr_head_linear.argtypes = [p, i, i, p, i, i, p, i, i, i, i, i, p]
         for name in ("oxr_stream_rms_norm", "oxr_norm_add_norm", "oxr_concat2_cast", "oxr_add_row_f32", "oxr_clamped_glu", "oxr_rotary_angles",
@@ -1093,7 +1093,7 @@ def mamba_conv(proj: torch.Tensor, col0: int, channels: int, weight: torch.Tenso
 def mamba_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_col0: int, *, heads: int, vdim: int, state: int, groups: int, dt_bias: torch.Tensor,
                a_log: torch.Tensor, d_skip: torch.Tensor, ssm: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, n_requests: int) -> torch.Tensor:
     """The selective-state recurrence over a packed step: fp32 ``y [tokens, heads * vdim]``; ``ssm`` (fp32 view, first axis the slot, each
-    slot ``[heads, vdim, state]``) is read and left at the state after each request's last token."""
+    slot ``[heads, state, vdim]``) is read and left at the state after each request's last token."""
     _need(xbc, "xbc")
     _need(proj, "proj")
     if ssm.dtype != torch.float32 or ssm.stride(-1) != 1:
@@ -1120,16 +1120,23 @@ def gated_group_norm(y: torch.Tensor, proj: torch.Tensor, z_col0: int, weight: t
 
 
 # --------------------------------------------------------------------------------------------------- attention with mask and sizes as arguments
-def scatter_rows(pool: torch.Tensor, src: torch.Tensor, col0: int, width: int, slots: torch.Tensor, status: torch.Tensor) -> None:
-    """``pool[slots[t]] = src[t, col0 : col0 + width]`` for a pool ``[pages, page_size, ...]`` whose slot rows hold ``width`` values; slot -1 skips."""
+def scatter_rows(pool: torch.Tensor, src: torch.Tensor, col0: int, slots: torch.Tensor, status: torch.Tensor, pool2: torch.Tensor | None = None) -> None:
+    """``pool[slots[t]] = src[t, col0 : col0 + width]`` for a pool ``[pages, page_size, ...]`` whose slot rows hold ``width`` values; slot -1
+    skips. With ``pool2`` (the values beside the keys) the columns that follow go to its slot rows in the same launch."""
     _need(pool, "pool")
     _need(src, "src", pool.dtype)
     n_slots = pool.shape[0] * pool.shape[1]
     row = pool[0, 0].numel()
-    if width != row:
-        raise KernelError(f"scatter_rows: a slot holds {row} values, the source brings {width}")
-    _done(_lib().oxr_scatter_rows(pool.data_ptr(), row, n_slots, src.data_ptr(), src.shape[1], col0, width, slots.data_ptr(), src.shape[0],
-                                  _dtype_code(src), status.data_ptr(), _stream()), "scatter_rows")
+    row2 = 0
+    if pool2 is not None:
+        _need(pool2, "pool2", pool.dtype)
+        if pool2.shape[:2] != pool.shape[:2]:
+            raise KernelError("scatter_rows: the two pools differ in pages or page size")
+        row2 = pool2[0, 0].numel()
+    if col0 + row + row2 > src.shape[1]:
+        raise KernelError(f"scatter_rows: columns {col0}..{col0 + row + row2} are beyond the source's {src.shape[1]}")
+    _done(_lib().oxr_scatter_rows(pool.data_ptr(), row, n_slots, src.data_ptr(), src.shape[1], col0, row, slots.data_ptr(), src.shape[0],
+                                  _dtype_code(src), status.data_ptr(), _ptr(pool2), row2, row2, _stream()), "scatter_rows")
 
 
 def latent_prep(pool: torch.Tensor, down: torch.Tensor, rank: int, rot: int, weight: torch.Tensor, eps: float, q: torch.Tensor, heads: int,

@@ -19,7 +19,7 @@ class Mamba2(Mixer):
 
     then ``y * silu(z)``, RMS-normed in ``norm_groups`` equal parts (each by its own root mean square) times ``norm``, then ``W_o``.
 
-    Per request the mixer keeps one fp32 state row: S ``[heads, value_dim, state]`` followed by the convolution's last ``taps - 1``
+    Per request the mixer keeps one fp32 state row: S ``[heads, state, value_dim]`` followed by the convolution's last ``taps - 1``
     inputs ``[channels, taps - 1]``; zero for a new request, carried from step to step whatever the cut."""
 
     def __init__(self, runtime: Runtime, position: PositionEncoding | None, *, hidden_size: int, num_heads: int, value_dim: int, state: int,

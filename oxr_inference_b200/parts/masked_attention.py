@@ -98,9 +98,7 @@ class MaskedAttention(Mixer):
         if qkv.dtype != k_pool.dtype:
             qkv = ops.cast(qkv, k_pool.dtype)
         if cache.store:
-            q_cols, k_cols = self.H * self.DK, self.KV * self.DK
-            ops.scatter_rows(k_pool, qkv, q_cols, k_cols, group.slots, ctx.status)
-            ops.scatter_rows(v_pool, qkv, q_cols + k_cols, self.KV * self.DV, group.slots, ctx.status)
+            ops.scatter_rows(k_pool, qkv, self.H * self.DK, group.slots, ctx.status, pool2=v_pool)   # the k columns, then the v columns
         if self.tiled and qkv.dtype == torch.bfloat16:
             # keys and values of one size the tiled kernels are built for: tensor cores, split-KV for single tokens
             q = qkv[:, :self.H * self.DK].contiguous().view(ctx.n_tokens, self.H, self.DK)

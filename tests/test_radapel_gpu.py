@@ -386,6 +386,46 @@ def test_stream_kernels(dtype):
     assert torch.equal(both.float().cpu(), torch.cat([s.cpu(), stream], 1).to(dtype).float())
 
 
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("n", [5, 16, 17, 150])
+def test_per_head_linear(dtype, n):
+    """Few rows run the CUDA-core kernel, more rows (bfloat16) the tensor-core one; both against the plain product, with entries
+    of the output outside the written stretch left alone."""
+    from oxr_inference_b200 import ops
+
+    g = torch.Generator().manual_seed(n)
+    heads, n_in, n_out = 3, 48, 80
+    x = torch.randn(n, heads, n_in + 8, generator=g).to(dtype)
+    w = (torch.randn(heads, n_in, n_out, generator=g) * 0.2).to(dtype)
+    out = torch.full((n, heads, n_out + 5), 7.0, dtype=dtype)
+    got = ops.head_linear(out.to(DEV), 3, x.to(DEV), 8, w.to(DEV)).float().cpu()
+    want = torch.einsum("thi,hio->tho", x[:, :, 8:].double(), w.double())
+    assert (got[:, :, 3:3 + n_out] - want).abs().max() <= (1e-4 if dtype == torch.float32 else 3e-2) * want.abs().max()
+    assert torch.all(got[:, :, :3] == 7.0) and torch.all(got[:, :, 3 + n_out:] == 7.0)
+
+
+@pytest.mark.parametrize("hidden", [88, 4096 + 64, 20000])
+def test_wide_rows_through_the_vector_kernels(hidden):
+    from oxr_inference_b200 import ops
+
+    g = torch.Generator().manual_seed(hidden)
+    n = 7
+    stream = torch.randn(n, hidden, generator=g)
+    y = torch.randn(n, hidden, generator=g).to(torch.bfloat16)
+    w1, w2 = 1 + 0.1 * torch.randn(hidden, generator=g), 1 + 0.1 * torch.randn(hidden, generator=g)
+    s = stream.clone().to(DEV)
+    h = ops.norm_add_norm(s, y.to(DEV), w1.to(DEV), 1e-5, w2.to(DEV), 1e-6)
+    want_s = stream.double() + RP.rms_norm(y.double(), w1.double(), 1e-5)
+    assert (s.cpu() - want_s).abs().max() < 2e-5
+    assert (h.float().cpu() - RP.rms_norm(want_s, w2.double(), 1e-6)).abs().max() < 4e-2
+    s2 = stream.clone().to(DEV)
+    assert ops.norm_add_norm(s2, y.to(DEV), w1.to(DEV), 1e-5) is None and torch.equal(s2, s)
+    gu = (torch.randn(n, 2 * hidden, generator=g) * 2).to(torch.bfloat16)
+    got = ops.clamped_glu(gu.to(DEV), alpha=1.702, limit=1.1)
+    gate, up = gu[:, :hidden].double().clamp(max=1.1), gu[:, hidden:].double().clamp(-1.1, 1.1)
+    assert (got.float().cpu() - gate * torch.sigmoid(1.702 * gate) * (up + 1)).abs().max() < 2e-2
+
+
 def test_rotary_angles_are_exact_far_out():
     from oxr_inference_b200 import ops
 
