@@ -112,6 +112,24 @@ __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.lau
 
 inline int oxr_chain_kernels = 0;   // one per library: set through oxr_set_chain()
 
+// What the gated epilogue of a product computes from a gate sum g and an up sum u. kind 0: silu(g) * u. kind 1: with
+// g' = min(g, limit) and u' = clamp(u, -limit, limit): g' * sigmoid(alpha g') * (u' + 1). The launchers of the gated products
+// hand the library's current form to their kernels by value; oxr_set_gate_form() sets it (before each gated call).
+struct GateForm {
+    int kind;
+    float alpha;
+    float limit;
+};
+inline GateForm oxr_gate_form = {0, 1.f, 0.f};
+__device__ __forceinline__ float gate_apply(const GateForm& f, float g, float u) {
+    if (f.kind == 1) {
+        g = fminf(g, f.limit);
+        u = fminf(fmaxf(u, -f.limit), f.limit) + 1.f;
+        return __fdividef(g, 1.f + __expf(-f.alpha * g)) * u;
+    }
+    return __fdividef(g, 1.f + __expf(-g)) * u;   // the fast division: two ulp, far inside a bf16 step
+}
+
 template <typename... KArgs, typename... Args>
 static inline void oxr_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, bool chained, Args... args) {
     cudaLaunchConfig_t cfg = {};

@@ -333,3 +333,4 @@ OXR_API int oxr_cast(void* dst, const void* src, size_t n, int src_dtype, int ds
 // Whether the kernels of this library that are written for it are launched programmatically dependent on the kernel
 // before them (see common.cuh). Off until set.
 OXR_API void oxr_set_chain(int on) { oxr_chain_kernels = on ? 1 : 0; }
+OXR_API void oxr_set_gate_form(int kind, float alpha, float limit) { oxr_gate_form = GateForm{kind, alpha, limit}; }

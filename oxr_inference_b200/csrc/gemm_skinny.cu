@@ -39,7 +39,7 @@ constexpr int SKINNY_WARPS = 8;
 template <int TILES, typename TO, bool GATED = false>
 __global__ void __launch_bounds__(SKINNY_WARPS * 32, TILES <= 2 ? 2 : 1)
 gemm_skinny_kernel(TO* __restrict__ C, const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, int M,
-                   int N, int K) {
+                   int N, int K, const GateForm gate) {
     __shared__ float partial[SKINNY_WARPS][16][8 * TILES + 1];
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     const int g = lane >> 2, t = lane & 3;
@@ -98,10 +98,10 @@ gemm_skinny_kernel(TO* __restrict__ C, const __nv_bfloat16* __restrict__ X, cons
         for (int idx = threadIdx.x; idx < 8 * 8 * TILES; idx += SKINNY_WARPS * 32) {
             const int r = idx % 8, m = idx / 8;
             if (m < M && n0 + r + 8 < N) {
-                float gate = 0.f, up = 0.f;
+                float gate_sum = 0.f, up = 0.f;
 #pragma unroll
-                for (int w = 0; w < SKINNY_WARPS; ++w) { gate += partial[w][r][m]; up += partial[w][r + 8][m]; }
-                C[(size_t)m * (N / 2) + n0 / 2 + r] = Num<TO>::from_f32(__fdividef(gate, 1.f + __expf(-gate)) * up);
+                for (int w = 0; w < SKINNY_WARPS; ++w) { gate_sum += partial[w][r][m]; up += partial[w][r + 8][m]; }
+                C[(size_t)m * (N / 2) + n0 / 2 + r] = Num<TO>::from_f32(gate_apply(gate, gate_sum, up));
             }
         }
     } else {
@@ -125,7 +125,7 @@ OXR_API int oxr_gemm_skinny_bf16(void* C, const void* X, const void* W, int M, i
     const unsigned blocks = (N + 15) / 16;
     const int tiles = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
 #define LAUNCH(TL, TO) \
-    gemm_skinny_kernel<TL, TO, false><<<blocks, SKINNY_WARPS * 32, 0, stream>>>((TO*)C, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, M, N, K)
+    gemm_skinny_kernel<TL, TO, false><<<blocks, SKINNY_WARPS * 32, 0, stream>>>((TO*)C, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, M, N, K, oxr_gate_form)
 #define BY_TILES(TO)                    \
     switch (tiles) {                    \
         case 1: LAUNCH(1, TO); break;   \
@@ -148,7 +148,7 @@ OXR_API int oxr_gemm_skinny_gated_bf16(void* C, const void* X, const void* W, in
     if (M > 64 || N % 16 != 0 || K <= 0 || K % 8 != 0 || (uintptr_t)X % 16 != 0 || (uintptr_t)W % 16 != 0) return OXR_BAD_ARGUMENT;
     const unsigned blocks = N / 16;
     using bf = __nv_bfloat16;
-#define LAUNCH_GATED(TL) gemm_skinny_kernel<TL, bf, true><<<blocks, SKINNY_WARPS * 32, 0, stream>>>((bf*)C, (const bf*)X, (const bf*)W, M, N, K)
+#define LAUNCH_GATED(TL) gemm_skinny_kernel<TL, bf, true><<<blocks, SKINNY_WARPS * 32, 0, stream>>>((bf*)C, (const bf*)X, (const bf*)W, M, N, K, oxr_gate_form)
     if (M <= 8) LAUNCH_GATED(1);
     else if (M <= 16) LAUNCH_GATED(2);
     else if (M <= 32) LAUNCH_GATED(4);

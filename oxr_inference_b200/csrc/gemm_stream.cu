@@ -109,7 +109,7 @@ struct FuseArgs {
 template <int TILES, typename TO, bool GATED, bool ADD = false, bool SCALED = false>
 __global__ void __launch_bounds__(ST_THREADS, 1)
 gemm_stream_kernel(TO* __restrict__ C, const __nv_bfloat16* __restrict__ X, const __nv_bfloat16* __restrict__ W, int M, int N, int K,
-                   int stages, int* status, const FuseArgs fa) {
+                   int stages, int* status, const FuseArgs fa, const GateForm gate) {
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* ring = smem;                                                     // stages x ST_STAGE_BYTES
     float* partial = reinterpret_cast<float*>(ring + (size_t)stages * ST_STAGE_BYTES);   // [ST_WARPS][16][8 * TILES + 1]
@@ -271,11 +271,11 @@ gemm_stream_kernel(TO* __restrict__ C, const __nv_bfloat16* __restrict__ X, cons
             for (int idx = threadIdx.x; idx < 8 * 8 * TILES; idx += ST_WARPS * 32) {
                 const int r = idx % 8, m = idx / 8;
                 if (m < M && n0 + r + 8 < N) {
-                    float gate = 0.f, up = 0.f;
+                    float gate_sum = 0.f, up = 0.f;
 #pragma unroll
-                    for (int w = 0; w < ST_WARPS; ++w) { gate += partial[(w * 16 + r) * PW + m]; up += partial[(w * 16 + r + 8) * PW + m]; }
-                    if constexpr (SCALED) { gate *= s_inv[m]; up *= s_inv[m]; }
-                    C[(size_t)m * (N / 2) + n0 / 2 + r] = Num<TO>::from_f32(__fdividef(gate, 1.f + __expf(-gate)) * up);
+                    for (int w = 0; w < ST_WARPS; ++w) { gate_sum += partial[(w * 16 + r) * PW + m]; up += partial[(w * 16 + r + 8) * PW + m]; }
+                    if constexpr (SCALED) { gate_sum *= s_inv[m]; up *= s_inv[m]; }
+                    C[(size_t)m * (N / 2) + n0 / 2 + r] = Num<TO>::from_f32(gate_apply(gate, gate_sum, up));
                 }
             }
         } else if constexpr (ADD) {
@@ -353,7 +353,7 @@ int launch_stream(void* C, const void* X, const void* W, int M, int N, int K, in
     const int groups = (N + 15) / 16;
     const int blocks = groups < sms ? groups : sms;
     oxr_launch(gemm_stream_kernel<TILES, TO, GATED, ADD, SCALED>, dim3(blocks), dim3(ST_THREADS), smem, stream, true,
-               (TO*)C, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, M, N, K, stages, status, fa);
+               (TO*)C, (const __nv_bfloat16*)X, (const __nv_bfloat16*)W, M, N, K, stages, status, fa, oxr_gate_form);
     return oxr_launch_status();
 }
 }  // namespace

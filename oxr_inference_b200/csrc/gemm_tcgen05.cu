@@ -64,7 +64,7 @@ template <typename TO, bool SPLIT, bool GATED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     int M, int N, int K, int bn, int stages, int tmem_cols, int num_tiles, int splits, float* __restrict__ partial,
-                    unsigned int* __restrict__ tickets, int* status) {
+                    unsigned int* __restrict__ tickets, int* status, const GateForm gate) {
     static_assert(!(GATED && SPLIT), "the gated epilogue is the plain one's variant only");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms are 1024 B
@@ -207,7 +207,7 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
                         for (int j = 0; j < 8; ++j)
                             if (4 * j < count) reinterpret_cast<uint4*>(mine + c0)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                     } else if (n0 + c0 < N) {
-                        if constexpr (GATED) store_row_piece_gated<TO>(C + (size_t)row * (N / 2) + (n0 + c0) / 2, v, count, n0 + c0, N);
+                        if constexpr (GATED) store_row_piece_gated<TO>(C + (size_t)row * (N / 2) + (n0 + c0) / 2, v, count, n0 + c0, N, gate);
                         else store_row_piece<TO>(C + (size_t)row * N + n0 + c0, v, count, n0 + c0, N);
                     }
                 }
@@ -311,7 +311,7 @@ int launch(void* C, const void* X, const void* W, int M, int N, int K, int bn, i
     while (tmem_cols < 2 * bn) tmem_cols *= 2;
     dim3 grid((unsigned)(units < num_sms ? units : num_sms));   // one block per SM (its shared memory fills the SM)
     oxr_launch(gemm_tcgen05_kernel<TO, SPLIT, GATED>, grid, dim3(TC_THREADS), SMEM_BYTES, stream, true, (TO*)C, map_x, map_w, M, N, K, bn,
-               stages, tmem_cols, (int)tiles, splits, partial, tickets, status);
+               stages, tmem_cols, (int)tiles, splits, partial, tickets, status, oxr_gate_form);
     return oxr_launch_status();
 }
 }  // namespace

@@ -73,7 +73,7 @@ __device__ __forceinline__ void pair_tile_origin(int tile, int M, int N, int bn,
 template <typename TO, bool GATED>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(PAIR_THREADS, 1)
 gemm_tcgen05_pair_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
-                         int M, int N, int K, int bn, int stages, int tmem_cols, int num_tiles, int* status) {
+                         int M, int N, int K, int bn, int stages, int tmem_cols, int num_tiles, int* status, const GateForm gate) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms are 1024 B
     const int stage_size = pair_stage_bytes(bn);
@@ -199,7 +199,7 @@ gemm_tcgen05_pair_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap
                 if (count == 32) tmem_ld_32x32(acc_addr + (uint32_t)c0, v);
                 else tmem_ld_32x16(acc_addr + (uint32_t)c0, v);
                 if (row < M && n0 + c0 < N) {
-                    if constexpr (GATED) store_row_piece_gated<TO>(C + (size_t)row * (N / 2) + (n0 + c0) / 2, v, count, n0 + c0, N);
+                    if constexpr (GATED) store_row_piece_gated<TO>(C + (size_t)row * (N / 2) + (n0 + c0) / 2, v, count, n0 + c0, N, gate);
                     else store_row_piece<TO>(C + (size_t)row * N + n0 + c0, v, count, n0 + c0, N);
                 }
             }
@@ -253,7 +253,7 @@ int launch_pair(void* C, const void* X, const void* W, int M, int N, int K, int 
     while (tmem_cols < 2 * bn) tmem_cols *= 2;
     const unsigned pairs = (unsigned)(tiles < max_pairs ? tiles : max_pairs);
     oxr_launch(gemm_tcgen05_pair_kernel<TO, GATED>, dim3(2 * pairs), dim3(PAIR_THREADS), SMEM_BYTES, stream, true, (TO*)C, map_x, map_w, M, N, K,
-               bn, stages, tmem_cols, (int)tiles, status);
+               bn, stages, tmem_cols, (int)tiles, status, oxr_gate_form);
     return oxr_launch_status();
 }
 }  // namespace

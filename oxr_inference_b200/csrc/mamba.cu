@@ -59,7 +59,8 @@ __device__ __forceinline__ float softplus_f32(float v) { return fmaxf(v, 0.f) + 
 // p = 32 blockIdx.x + l, warp w the state entries n = 32 w .. 32 w + 31, so a thread keeps 32 entries of S in registers and
 // updates them with plain multiply-adds: B and C of a token are the same for all lanes and come from shared memory as
 // broadcast 16-byte loads, no shuffles. The step's tokens go through shared memory TT at a time (B, C, x, softplus and decay,
-// each computed once per token and block); the warps' partial sums of y meet there too and are added in the order of the warps.
+// each computed once per token and block; the next tile is fetched while this one is computed); the warps' partial sums of y
+// meet there too and are added in the order of the warps.
 // S is stored [heads, N, vdim]: the lanes of a warp read and write 128 contiguous bytes per state entry.
 template <typename T, int NW, int TT>
 __global__ void __launch_bounds__(32 * NW) ssm_scan_kernel(
@@ -86,42 +87,70 @@ __global__ void __launch_bounds__(32 * NW) ssm_scan_kernel(
     for (int k = 0; k < 32; ++k) s[k] = (n0 + k < N && p < vdim) ? S[(size_t)(n0 + k) * vdim + p] : 0.f;
     const float neg_a = -expf(a_log[h]), bias = dt_bias[h], skip = d_skip[h];
 
-    for (int tile = t0; tile < t1; tile += TT) {
+    // A tile's inputs are fetched into registers while the tile before it is computed (all loads of a tile are issued back to
+    // back: one trip to memory per tile, hidden behind the sums), then written to shared memory between two barriers.
+    constexpr int XPT = (TT + NW - 1) / NW;           // x values per thread and tile
+    const int n = threadIdx.x;                        // this thread's state entry in the fetch (NP threads, NP entries)
+    T bv[TT], cv[TT], xv[XPT], dtv = Num<T>::from_f32(0.f);
+    auto fetch = [&](int tile) {
         const int nt = min(TT, t1 - tile);
-        for (int i = threadIdx.x; i < nt * NP; i += 32 * NW) {
-            const int t = i / NP, n = i % NP;
-            const T* row = xbc + (size_t)(tile + t) * channels;
-            Bs[i] = n < N ? Num<T>::to_f32(row[b_col + n]) : 0.f;
-            Cs[i] = n < N ? Num<T>::to_f32(row[c_col + n]) : 0.f;
+#pragma unroll
+        for (int t = 0; t < TT; ++t) {
+            const bool ok = t < nt && n < N;
+            const T* row = xbc + (size_t)(tile + (t < nt ? t : 0)) * channels;
+            bv[t] = ok ? row[b_col + n] : Num<T>::from_f32(0.f);
+            cv[t] = ok ? row[c_col + n] : Num<T>::from_f32(0.f);
         }
-        for (int i = threadIdx.x; i < nt * 32; i += 32 * NW) {
-            const int t = i >> 5, c = i & 31;
-            xs[i] = (p0 + c < vdim) ? Num<T>::to_f32(xbc[(size_t)(tile + t) * channels + h * vdim + p0 + c]) : 0.f;
+#pragma unroll
+        for (int j = 0; j < XPT; ++j) {
+            const int i = threadIdx.x + j * 32 * NW, t = i >> 5, c = i & 31;
+            xv[j] = (t < nt && p0 + c < vdim) ? xbc[(size_t)(tile + t) * channels + h * vdim + p0 + c] : Num<T>::from_f32(0.f);
         }
-        if (threadIdx.x < nt) {
-            const float dt = softplus_f32(Num<T>::to_f32(proj[(size_t)(tile + threadIdx.x) * proj_stride + dt_col0 + h]) + bias);
+        if ((int)threadIdx.x < nt) dtv = proj[(size_t)(tile + threadIdx.x) * proj_stride + dt_col0 + h];
+    };
+    auto stash = [&](int tile) {
+        const int nt = min(TT, t1 - tile);
+#pragma unroll
+        for (int t = 0; t < TT; ++t) {
+            Bs[t * NP + n] = Num<T>::to_f32(bv[t]);
+            Cs[t * NP + n] = Num<T>::to_f32(cv[t]);
+        }
+#pragma unroll
+        for (int j = 0; j < XPT; ++j) {
+            const int i = threadIdx.x + j * 32 * NW;
+            if (i < TT * 32) xs[i] = Num<T>::to_f32(xv[j]);
+        }
+        if ((int)threadIdx.x < nt) {
+            const float dt = softplus_f32(Num<T>::to_f32(dtv) + bias);
             dts[threadIdx.x] = dt;
             decays[threadIdx.x] = expf(neg_a * dt);
         }
-        __syncthreads();
+    };
+    fetch(t0);
+    stash(t0);
+    __syncthreads();
+    for (int tile = t0; tile < t1; tile += TT) {
+        const int nt = min(TT, t1 - tile);
+        const bool more = tile + TT < t1;
+        if (more) fetch(tile + TT);
         for (int t = 0; t < nt; ++t) {
             const float decay = decays[t], dx = dts[t] * xs[t * 32 + lane];
             const float4* b4 = reinterpret_cast<const float4*>(Bs + t * NP + n0);
             const float4* c4 = reinterpret_cast<const float4*>(Cs + t * NP + n0);
-            float sum = 0.f;
+            float sum[4] = {0.f, 0.f, 0.f, 0.f};   // four chains instead of one of 32 dependent multiply-adds; added in a fixed order
 #pragma unroll
             for (int k4 = 0; k4 < 8; ++k4) {
                 const float4 b = b4[k4], c = c4[k4];
                 s[4 * k4] = fmaf(decay, s[4 * k4], dx * b.x);
-                sum = fmaf(s[4 * k4], c.x, sum);
+                sum[0] = fmaf(s[4 * k4], c.x, sum[0]);
                 s[4 * k4 + 1] = fmaf(decay, s[4 * k4 + 1], dx * b.y);
-                sum = fmaf(s[4 * k4 + 1], c.y, sum);
+                sum[1] = fmaf(s[4 * k4 + 1], c.y, sum[1]);
                 s[4 * k4 + 2] = fmaf(decay, s[4 * k4 + 2], dx * b.z);
-                sum = fmaf(s[4 * k4 + 2], c.z, sum);
+                sum[2] = fmaf(s[4 * k4 + 2], c.z, sum[2]);
                 s[4 * k4 + 3] = fmaf(decay, s[4 * k4 + 3], dx * b.w);
-                sum = fmaf(s[4 * k4 + 3], c.w, sum);
+                sum[3] = fmaf(s[4 * k4 + 3], c.w, sum[3]);
             }
-            part[(t * NW + warp) * 32 + lane] = sum;
+            part[(t * NW + warp) * 32 + lane] = (sum[0] + sum[1]) + (sum[2] + sum[3]);
         }
         __syncthreads();
         for (int i = threadIdx.x; i < nt * 32; i += 32 * NW) {
@@ -132,7 +161,10 @@ __global__ void __launch_bounds__(32 * NW) ssm_scan_kernel(
             for (int w = 0; w < NW; ++w) v += part[(t * NW + w) * 32 + c];
             y[(size_t)(tile + t) * inner + h * vdim + p0 + c] = fmaf(skip, xs[i], v);
         }
-        __syncthreads();   // the tile's buffers are free for the next one
+        if (!more) break;
+        __syncthreads();   // everyone has read this tile's buffers
+        stash(tile + TT);
+        __syncthreads();
     }
     if (p < vdim) {
 #pragma unroll

@@ -106,12 +106,12 @@ __device__ __forceinline__ void store_row_piece(TO* dst, const uint32_t (&v)[32]
 // silu(gate) * up (oxr_runtime/language.py:102-104), `count / 2` values, into a row of N / 2 columns. `dst` points at
 // column col0 / 2 of that row.
 template <typename TO>
-__device__ __forceinline__ void store_row_piece_gated(TO* dst, const uint32_t (&v)[32], int count, int col0, int N) {
+__device__ __forceinline__ void store_row_piece_gated(TO* dst, const uint32_t (&v)[32], int count, int col0, int N, const GateForm& gate) {
     float o[16];
 #pragma unroll
     for (int j = 0; j < 16; ++j) {
         const float g = __uint_as_float(v[(j / 8) * 16 + j % 8]), u = __uint_as_float(v[(j / 8) * 16 + 8 + j % 8]);
-        o[j] = __fdividef(g, 1.f + __expf(-g)) * u;   // the fast division: two ulp, far inside a bf16 step
+        o[j] = gate_apply(gate, g, u);
     }
     const int outs = count / 2;
     if (col0 + count <= N && ((uintptr_t)dst % 16 == 0)) {

@@ -149,6 +149,8 @@ def _lib():
         lib.oxr_set_chain.argtypes = [c_int]
         lib.oxr_set_chain.restype = None
         lib.oxr_set_chain(int(CHAIN_KERNELS))
+        lib.oxr_set_gate_form.argtypes = [c_int, c_float, c_float]
+        lib.oxr_set_gate_form.restype = None
         _core = lib
     return _core
 
@@ -298,11 +300,22 @@ as its rows g and g + 8."""
 
 
 def gated_silu_linear(x: torch.Tensor, weight: torch.Tensor, interleave: int = 0) -> torch.Tensor:
-    """``silu(x Wg^T) * (x Wu^T)`` for a weight that stacks Wg and Wu: side by side (``interleave`` 0: one product,
-    then the SiLU kernel) or alternating in groups of 8 rows. With alternating rows a bf16 product runs the kernel
-    ``linear`` would pick for its size (skinny, one-SM or two-SM tcgen05) with an epilogue that applies SiLU to the fp32
-    sums and writes the gated product alone; 32-bit runs the product and then the SiLU kernel on interleaved columns.
+    """``silu(x Wg^T) * (x Wu^T)``: :func:`gated_linear` with the SiLU form."""
+    return gated_linear(x, weight, interleave)
+
+
+GATE_KINDS = {"silu": 0, "clamped": 1}
+
+
+def gated_linear(x: torch.Tensor, weight: torch.Tensor, interleave: int = 0, *, kind: str = "silu", alpha: float = 1.0,
+                 limit: float = 0.0) -> torch.Tensor:
+    """``gate_form(x Wg^T, x Wu^T)`` for a weight that stacks Wg and Wu: side by side (``interleave`` 0: one product,
+    then the activation kernel) or alternating in groups of 8 rows. ``kind`` "silu": ``silu(g) * u``; "clamped": with ``g' = min(g, limit)``
+    and ``u' = clamp(u, -limit, limit)``, ``g' * sigmoid(alpha g') * (u' + 1)``. With alternating rows a bf16 product runs the kernel
+    ``linear`` would pick for its size (skinny, one-SM or two-SM tcgen05) with an epilogue that applies the form to the fp32
+    sums and writes the gated product alone; 32-bit runs the product and then the activation kernel on interleaved columns.
     ``x`` may be a :class:`NormedLazily`."""
+    _lib().oxr_set_gate_form(GATE_KINDS[kind], float(alpha), float(limit))   # read by the gated launchers below, handed to their kernels by value
     if isinstance(x, NormedLazily):
         out = _scaled_linear(x, weight, gated=True) if interleave == GATE_UP_INTERLEAVE else None
         if out is not None:
@@ -330,7 +343,9 @@ def gated_silu_linear(x: torch.Tensor, weight: torch.Tensor, interleave: int = 0
             _done(lib.oxr_gemm_tcgen05_gated_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, tile_n,
                                                   new_status(x.device).data_ptr(), _stream()), "gemm_tcgen05_gated")
         return out
-    return silu_mul(linear(x, weight), interleave)
+    if kind == "silu":
+        return silu_mul(linear(x, weight), interleave)
+    return clamped_glu(linear(x, weight), alpha=alpha, limit=limit, interleave=interleave)
 
 
 def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:

@@ -49,11 +49,12 @@ class SwiGLU(FeedForward):
 class ClampedGLU(FeedForward):
     """``down( g sigmoid(alpha g) (u + 1) )`` with ``g = min(h W_gate^T, limit)`` and ``u = clamp(h W_up^T, -limit, limit)``: a gated unit
     whose gate is a sigmoid-approximated GELU (``alpha`` = 1.702), whose linear branch is shifted by one and whose two branches are
-    clamped. Gate and up are one product."""
+    clamped. Gate and up are one product whose epilogue applies the activation (bfloat16, sizes that allow it)."""
 
     def __init__(self, runtime: Runtime, *, hidden_size: int, intermediate_size: int, limit: float, alpha: float = 1.702):
         self.hidden, self.inter, self.limit, self.alpha = int(hidden_size), int(intermediate_size), float(limit), float(alpha)
-        self.gate_up = StackedLinear(runtime, self.hidden, {"gate": self.inter, "up": self.inter})
+        # rows alternate in groups of 8 where the size allows, as in SwiGLU: the products' epilogues then apply the gate form
+        self.gate_up = StackedLinear(runtime, self.hidden, {"gate": self.inter, "up": self.inter}, interleave=ops.GATE_UP_INTERLEAVE)
         self.down = StackedLinear(runtime, self.inter, {"down": self.hidden})
 
     def parameters(self) -> dict[str, ParamInfo]:
@@ -68,4 +69,4 @@ class ClampedGLU(FeedForward):
             raise KeyError(name)
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
-        return self.down(ops.clamped_glu(self.gate_up(h), alpha=self.alpha, limit=self.limit, interleave=self.gate_up.interleave))
+        return self.down(ops.gated_linear(h, self.gate_up.weight, self.gate_up.interleave, kind="clamped", alpha=self.alpha, limit=self.limit))
