@@ -280,7 +280,6 @@ def design_throughput(cfg: dict, vocab: int, K: int, W: int, batch: int, context
     torch.cuda.synchronize()
     ms = start.elapsed_time(end) / K
     engine.runner.check()
-    weights = sum(t.numel() * t.element_size() for part in engine.runner.model.parts() for t in vars(part).values() if isinstance(t, torch.Tensor))
     return {"prefill_tok_s": round(prefill_tokens / (prefill_ms * 1e-3), 1), "prefill_ms": round(prefill_ms, 3), "prefill_launches": prefill_launches,
             "decode_tok_s": round(batch * 1000.0 / ms, 1), "decode_ms_per_step": round(ms, 4), "decode_launches_per_step": engine.graphs.kernels_per_replay[key]}
 

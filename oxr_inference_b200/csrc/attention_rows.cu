@@ -15,9 +15,10 @@
 // beside the rotated shared key part, with the queries' rotated parts turned in place) and a per-head linear map.
 #include "common.cuh"
 
-constexpr int ROWS_MAX_DV_CHUNKS = 16;   // DV <= 512
+constexpr int ROWS_MAX_DV_CHUNKS = 32;   // DV <= 1024
 
-template <typename T>
+// DVC: 32-wide pieces of a value row that a lane accumulates (DV <= 32 * DVC).
+template <typename T, int DVC>
 __global__ void __launch_bounds__(128) attn_rows_kernel(
     T* __restrict__ out, const T* __restrict__ q, int q_stride, const T* __restrict__ k_pool, long long k_slot_stride, int k_head_stride,
     const T* __restrict__ v_pool, long long v_slot_stride, int v_head_stride, int DK, int DV, int H, int KVH, const int* __restrict__ positions,
@@ -39,9 +40,9 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(
 
     float m = -INFINITY, l = 0.f;
     if (sink != nullptr) { m = sink[h]; l = 1.f; }   // a key with score sink[h] and no value
-    float acc[ROWS_MAX_DV_CHUNKS];
+    float acc[DVC];
 #pragma unroll
-    for (int i = 0; i < ROWS_MAX_DV_CHUNKS; ++i) acc[i] = 0.f;
+    for (int i = 0; i < DVC; ++i) acc[i] = 0.f;
 
     for (int j0 = lo; j0 <= p; j0 += 32) {
         const int j = j0 + lane;
@@ -71,14 +72,14 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(
         l = l * corr + warp_sum(w);
         m = m_new;
 #pragma unroll
-        for (int i = 0; i < ROWS_MAX_DV_CHUNKS; ++i) acc[i] *= corr;
+        for (int i = 0; i < DVC; ++i) acc[i] *= corr;
         const int count = min(32, p - j0 + 1);
         for (int jj = 0; jj < count; ++jj) {
             const float wj = __shfl_sync(0xffffffffu, w, jj);
             const long long sj = __shfl_sync(0xffffffffu, slot, jj);
             const T* vr = v_pool + sj * v_slot_stride + (long long)kvh * v_head_stride;
 #pragma unroll
-            for (int i = 0; i < ROWS_MAX_DV_CHUNKS; ++i) {
+            for (int i = 0; i < DVC; ++i) {
                 const int d = lane + 32 * i;
                 if (d < DV) acc[i] = fmaf(wj, Num<T>::to_f32(vr[d]), acc[i]);
             }
@@ -87,7 +88,7 @@ __global__ void __launch_bounds__(128) attn_rows_kernel(
     const float inv = l > 0.f ? 1.f / l : 0.f;
     T* o = out + ((size_t)t * H + h) * DV;
 #pragma unroll
-    for (int i = 0; i < ROWS_MAX_DV_CHUNKS; ++i) {
+    for (int i = 0; i < DVC; ++i) {
         const int d = lane + 32 * i;
         if (d < DV) o[d] = Num<T>::from_f32(acc[i] * inv);
     }
@@ -107,16 +108,21 @@ OXR_API int oxr_attention_rows(void* out, const void* q, int q_stride, const voi
     if (grid.y > 65535) return OXR_BAD_ARGUMENT;
     const size_t smem = (size_t)warps * DK * sizeof(float);
     if (smem > 48 * 1024) return OXR_BAD_ARGUMENT;
-    if (dtype == 0)
-        attn_rows_kernel<float><<<grid, 32 * warps, smem, stream>>>((float*)out, (const float*)q, q_stride, (const float*)k_pool, k_slot_stride, k_head_stride,
-                                                                   (const float*)v_pool, v_slot_stride, v_head_stride, DK, DV, H, KVH, positions,
-                                                                   req_of_token, block_table, table_width, page_size, num_pages, scale, chunk, window,
-                                                                   dist_bias, bias_rows, sink, status);
-    else
-        attn_rows_kernel<__nv_bfloat16><<<grid, 32 * warps, smem, stream>>>(
-            (__nv_bfloat16*)out, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)k_pool, k_slot_stride, k_head_stride,
-            (const __nv_bfloat16*)v_pool, v_slot_stride, v_head_stride, DK, DV, H, KVH, positions, req_of_token, block_table, table_width, page_size,
-            num_pages, scale, chunk, window, dist_bias, bias_rows, sink, status);
+#define OXR_ROWS(T, DVC) \
+    attn_rows_kernel<T, DVC><<<grid, 32 * warps, smem, stream>>>((T*)out, (const T*)q, q_stride, (const T*)k_pool, k_slot_stride, k_head_stride, \
+                                                                (const T*)v_pool, v_slot_stride, v_head_stride, DK, DV, H, KVH, positions, req_of_token, \
+                                                                block_table, table_width, page_size, num_pages, scale, chunk, window, dist_bias, \
+                                                                bias_rows, sink, status)
+    if (dtype == 0) {
+        if (DV <= 128) OXR_ROWS(float, 4);
+        else if (DV <= 512) OXR_ROWS(float, 16);
+        else OXR_ROWS(float, 32);
+    } else {
+        if (DV <= 128) OXR_ROWS(__nv_bfloat16, 4);
+        else if (DV <= 512) OXR_ROWS(__nv_bfloat16, 16);
+        else OXR_ROWS(__nv_bfloat16, 32);
+    }
+#undef OXR_ROWS
     return oxr_launch_status();
 }
 

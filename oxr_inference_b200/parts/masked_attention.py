@@ -188,7 +188,10 @@ class LatentAttention(Mixer):
         q_cols = H * (D + R)
         q = both[:, :q_cols].contiguous().view(n, H, D + R)
         down = both[:, q_cols:].contiguous()
-        cos, sin = self.position.step_angles(ctx)
+        if self.position is not None:
+            cos, sin = self.position.step_angles(ctx)
+        else:   # no rotated part at all
+            cos = sin = torch.empty((n, 0), dtype=torch.float32, device=pool.device)
         q_abs = torch.empty((n, H, L + R), dtype=pool.dtype, device=pool.device)
         ops.latent_prep(pool, down, L, R, self.c_norm, self.eps, q, H, D + R, D, q_abs, L + R, L, cos, sin,
                         group.slots if cache.store else ctx.no_store_slots, ctx.status)

@@ -92,8 +92,9 @@ def latent_attention(h: torch.Tensor, w: dict, p: str, m: dict, eps: float) -> t
     q = (h @ w[p + "q"].T).view(T, H, D + R)
     down = h @ w[p + "dkv"].T
     c = rms_norm(down[:, :L], w[p + "dkv.norm"], eps)
-    k_rot = rotate_pairs(down[:, L:].view(T, 1, R), pos, m["rot"]["dims"], m["rot"]["base"])[:, 0]
-    q_rot = rotate_pairs(q[..., D:], pos, m["rot"]["dims"], m["rot"]["base"])
+    rot = m.get("rot") or {"dims": 0, "base": 1.0}
+    k_rot = rotate_pairs(down[:, L:].view(T, 1, R), pos, rot["dims"], rot["base"])[:, 0]
+    q_rot = rotate_pairs(q[..., D:], pos, rot["dims"], rot["base"])
     k_plain = (c @ w[p + "uk"].T).view(T, H, D)
     v = (c @ w[p + "uv"].T).view(T, H, DV)
     sink = w[p + "sink"]

@@ -62,6 +62,9 @@ SINGLE = {
     "tiled_chunk_of_three": RU.model_config([RU.attention_layer(heads=2, kv_heads=2, dim=48, vdim=48, chunk=3, bias_max=0, mlp=None)]),
     "latent_sink": RU.model_config([RU.latent_layer(mlp=None)]),
     "latent_not_tiled": RU.model_config([RU.latent_layer(kv_rank=20, mlp=None)]),
+    "latent_nothing_rotated": RU.model_config([{"type": "latent_attention", "mlp": None, "mixer": {
+        "heads": 3, "dim": 16, "rot_dim": 0, "vdim": 8, "kv_rank": 24, "scale": 0.3}}]),
+    "latent_wide_row": RU.model_config([RU.latent_layer(heads=2, dim=16, rot_dim=8, rot_dims=8, vdim=16, kv_rank=600, mlp=None)]),
     "latent_part_rotated": RU.model_config([RU.latent_layer(heads=5, dim=24, rot_dim=12, rot_dims=6, vdim=20, kv_rank=36, mlp=None)], width=56),
     "mamba2": RU.model_config([RU.mamba_layer()]),
     "mamba2_one_group_wide_state": RU.model_config([RU.mamba_layer(heads=3, vdim=5, state=130, groups=1, conv=5, norm_groups=1)]),
@@ -300,14 +303,15 @@ def test_keys_seen_and_not_seen(case, dtype):
     assert (shifted - want).abs().max() > 0.1
 
 
-@pytest.mark.parametrize("case", ["chunk_bias", "sink", "window_chunk"])
-def test_keys_seen_and_not_seen_by_the_tiled_kernels(case):
+@pytest.mark.parametrize("case,D", [("chunk_bias", 32), ("sink", 32), ("window_chunk", 32), ("chunk_bias", 96), ("sink", 144), ("chunk_bias", 192),
+                                    ("window_chunk", 224), ("sink", 256)])
+def test_keys_seen_and_not_seen_by_the_tiled_kernels(case, D):
     """The same marked keys through the tensor-core kernels (bfloat16, keys and values of one size): a prompt's portion that crosses
     chunk edges (long tiles), a short portion, and single tokens of several requests with split keys."""
     from oxr_inference_b200 import ops
 
     g = torch.Generator().manual_seed(7)
-    H, KV, D, P, ctx = 4, 2, 32, 8, 300
+    H, KV, P, ctx = 4, 2, 8, 300
     chunk, window, bias, sink = 0, 0, None, None
     if case == "chunk_bias":
         chunk, bias = 20, torch.randn(9, H, generator=g)
