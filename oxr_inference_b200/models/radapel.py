@@ -175,6 +175,6 @@ def radapel_model_spec(c: RadapelConfig, tensor_shapes: Mapping[str, tuple[int, 
         max_positions=MAX_POSITIONS, eos_token_ids=c.eos_token_ids)
 
 
-DEFAULT_BIAS_ROWS = 32
+DEFAULT_BIAS_ROWS = 16
 
 RADAPEL = register_architecture(Architecture("Radapel", RadapelConfig.from_dict, radapel_model_spec, shapes_matter=True))
