@@ -34,30 +34,45 @@ class CachePlan:
     entries: tuple[EntryPlan, ...]
 
 
-def make_cache_plan(needs: list[PagedKVNeed | StateNeed | None], cache_of: list[int | None]) -> CachePlan:
-    """``needs[i]``: what schedule entry i's mixer keeps; ``cache_of[i]``: the entry whose cache it reads instead."""
+def split_need(need, where: str = "") -> tuple[PagedKVNeed | None, StateNeed | None]:
+    """A mixer's need as (paged part, state part): it may keep pages, a fixed-size state, both (given as a pair) or nothing."""
+    paged = state = None
+    for one in (need if isinstance(need, (tuple, list)) else (need,)):
+        if one is None:
+            continue
+        if isinstance(one, PagedKVNeed) and paged is None:
+            paged = one
+        elif isinstance(one, StateNeed) and state is None:
+            state = one
+        else:
+            raise TypeError(f"{where}unknown or repeated cache need {one!r}")
+    return paged, state
+
+
+def make_cache_plan(needs: list, cache_of: list[int | None]) -> CachePlan:
+    """``needs[i]``: what schedule entry i's mixer keeps (a :class:`PagedKVNeed`, a :class:`StateNeed`, a pair of both, or None);
+    ``cache_of[i]``: the entry whose cache it reads instead."""
     groups: list[list] = []  # [need, layer count]
     states: list[StateNeed] = []
     entries: list[EntryPlan | None] = [None] * len(needs)
     for i, (need, src) in enumerate(zip(needs, cache_of)):
         if src is not None:
             continue
-        if isinstance(need, PagedKVNeed):
+        paged, fixed = split_need(need, f"schedule entry {i}: ")
+        group = layer_in_group = state = None
+        if paged is not None:
             for g, (have, count) in enumerate(groups):
-                if have == need:
-                    entries[i] = EntryPlan(group=g, layer_in_group=count)
+                if have == paged:
+                    group, layer_in_group = g, count
                     groups[g][1] += 1
                     break
             else:
-                groups.append([need, 1])
-                entries[i] = EntryPlan(group=len(groups) - 1, layer_in_group=0)
-        elif isinstance(need, StateNeed):
-            states.append(need)
-            entries[i] = EntryPlan(state=len(states) - 1)
-        elif need is None:
-            entries[i] = EntryPlan()
-        else:
-            raise TypeError(f"schedule entry {i}: unknown cache need {need!r}")
+                groups.append([paged, 1])
+                group, layer_in_group = len(groups) - 1, 0
+        if fixed is not None:
+            states.append(fixed)
+            state = len(states) - 1
+        entries[i] = EntryPlan(group=group, layer_in_group=layer_in_group or 0, state=state)
     for i, src in enumerate(cache_of):
         if src is None:
             continue

@@ -138,9 +138,17 @@ def _lib():
         lib.oxr_scatter_rows.argtypes = [p, ll, ll, p, i, i, i, p, i, i, p, p, ll, i, p]
         lib.oxr_latent_prep.argtypes = [p, ll, ll, p, i, i, p, f, p, i, i, i, p, i, i, p, p, i, p, i, i, p, p]
         lib.oxr_head_linear.argtypes = [p, i, i, p, i, i, p, i, i, i, i, i, p]
+        lib.oxr_conv_qkv_store.argtypes = [p, p, p, i, i, i, i, i, i, i, p, p, p, ll, p, p, p, p, f, i, p, p, p, p, p, ll, i, p, p]
+        lib.oxr_add_bias.argtypes = [p, p, i, i, i, p]
+        lib.oxr_scale_f32.argtypes = [p, f, ll, p]
+        lib.oxr_mlstm_scan.argtypes = [p, p, i, i, i, i, i, p, p, i, i, i, f, f, p, ll, p, p, i, p]
+        lib.oxr_head_norm_gate.argtypes = [p, p, p, i, i, i, p, i, i, f, i, p]
+        lib.oxr_route.argtypes = [p, p, p, p, i, i, i, i, i, f, p]
+        lib.oxr_gated_relu2.argtypes = [p, p, p, i, i, i, i, p]
         for name in ("oxr_stream_rms_norm", "oxr_norm_add_norm", "oxr_concat2_cast", "oxr_add_row_f32", "oxr_clamped_glu", "oxr_rotary_angles",
                      "oxr_mamba_conv", "oxr_mamba_scan", "oxr_gated_group_norm", "oxr_attention_rows", "oxr_scatter_rows", "oxr_latent_prep",
-                     "oxr_head_linear"):
+                     "oxr_head_linear", "oxr_conv_qkv_store", "oxr_add_bias", "oxr_scale_f32", "oxr_mlstm_scan", "oxr_head_norm_gate", "oxr_route",
+                     "oxr_gated_relu2"):
             getattr(lib, name).restype = c_int
         for name in ("oxr_embedding", "oxr_add_rms_norm", "oxr_silu_mul", "oxr_cast", "oxr_qk_norm_rope_store",
                      "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_gemm_skinny_gated_bf16", "oxr_gemm_stream_bf16", "oxr_gemm_stream_gated_bf16", "oxr_gemm_tcgen05_bf16", "oxr_gemm_tcgen05_pair_bf16", "oxr_gemm_tcgen05_gated_bf16", "oxr_gemm_few_rows_cluster_bf16", "oxr_gemm_few_rows_max_clusters",
@@ -1228,3 +1236,136 @@ def attention_rows(q: torch.Tensor, num_heads: int, k_pool: torch.Tensor, v_pool
                                     float(scale), int(chunk), int(window), _ptr(dist_bias), bias_rows, _ptr(sink), _dtype_code(q), status.data_ptr(),
                                     _stream()), "attention_rows")
     return out
+
+
+# --------------------------------------------------------------------------------------------------- convolved q|k|v, biases
+def conv_qkv_store(proj: torch.Tensor, cq: int, ck: int, cv: int, *, conv: torch.Tensor | None, bias: torch.Tensor | None, tails: torch.Tensor | None,
+                   k_pool: torch.Tensor, v_pool: torch.Tensor, slots: torch.Tensor, req_of_token: torch.Tensor, cu_q: torch.Tensor,
+                   state_slots: torch.Tensor, positions: torch.Tensor, n_requests: int, status: torch.Tensor, temp_coef: float = 0.0,
+                   temp_every: int = 0, blend: torch.Tensor | None = None, first: torch.Tensor | None = None, keep_values: bool = False
+                   ) -> tuple[torch.Tensor, torch.Tensor | None]:
+    """From a packed step's stacked projection ``proj [tokens, >= cq + ck + cv]`` to queries and cache rows in one launch (and one more that
+    rolls the tails): add ``bias [cq + ck + cv]``, filter every channel causally with ``conv [channels, taps]`` (the last tap meets the current
+    token; what stands before a step's first token comes from the request's ``tails`` row ``[channels, taps - 1]``, zero for a new request,
+    which is rolled forward), multiply the queries by ``1 + temp_coef ln(floor((p + 1) / temp_every) + 1)`` (``temp_every`` 0: not), blend the
+    values as ``(1 - blend) v + blend first`` (``blend``: one fp32 number on the device; ``first [tokens, cv]``), and write keys and values to
+    ``k_pool`` / ``v_pool`` (one layer's ``[pages, page_size, KV, D]``) at ``slots`` (-1 skips). ``conv`` None: no filter. Returns the queries
+    ``[tokens, cq]`` and, with ``keep_values``, the values ``[tokens, cv]`` as they were cached."""
+    _need(proj, "proj")
+    _need(k_pool, "k_pool", proj.dtype)
+    _need(v_pool, "v_pool", proj.dtype)
+    n, channels = proj.shape[0], cq + ck + cv
+    taps = 0
+    if conv is not None:
+        _need(conv, "conv", torch.float32)
+        if conv.shape[0] != channels:
+            raise KernelError(f"conv_qkv_store: the filter has {conv.shape[0]} channels for {channels}")
+        taps = conv.shape[1]
+    if bias is not None:
+        _need(bias, "bias", torch.float32)
+        if bias.numel() != channels:
+            raise KernelError("conv_qkv_store: one bias per channel")
+    if taps > 1:
+        if tails is None or tails.dtype != torch.float32 or tails.stride(-1) != 1 or tails[0].numel() < channels * (taps - 1):
+            raise KernelError("conv_qkv_store: the tails must be fp32 rows of channels x (taps - 1) with a dense last axis")
+    if k_pool[0, 0].numel() != ck or v_pool[0, 0].numel() != cv or k_pool.shape[:2] != v_pool.shape[:2]:
+        raise KernelError("conv_qkv_store: the pools do not fit the key and value columns")
+    if blend is not None:
+        _need(blend, "blend", torch.float32)
+        _need(first, "first", proj.dtype)
+        if first.shape != (n, cv):
+            raise KernelError("conv_qkv_store: the values to blend with must be [tokens, cv]")
+    q = torch.empty((n, cq), dtype=proj.dtype, device=proj.device)
+    v = torch.empty((n, cv), dtype=proj.dtype, device=proj.device) if keep_values else None
+    _done(_lib().oxr_conv_qkv_store(q.data_ptr(), _ptr(v), proj.data_ptr(), n, n_requests, proj.shape[1], cq, ck, cv, taps, _ptr(conv), _ptr(bias),
+                                    _ptr(tails), tails.stride(0) if tails is not None else 0, req_of_token.data_ptr(), cu_q.data_ptr(),
+                                    state_slots.data_ptr(), positions.data_ptr(), float(temp_coef), int(temp_every), _ptr(blend), _ptr(first),
+                                    k_pool.data_ptr(), v_pool.data_ptr(), slots.data_ptr(), k_pool.shape[0] * k_pool.shape[1], _dtype_code(proj),
+                                    status.data_ptr(), _stream()), "conv_qkv_store")
+    global launch_count
+    launch_count += 1 if taps > 1 else 0
+    return q, v
+
+
+def add_bias_(x: torch.Tensor, row: torch.Tensor) -> torch.Tensor:
+    """``x[t] += row`` in place (the sum in fp32)."""
+    _need(x, "x")
+    _need(row, "row", torch.float32)
+    if x.dim() != 2 or row.numel() != x.shape[1]:
+        raise KernelError("add_bias_: one entry per column")
+    _done(_lib().oxr_add_bias(x.data_ptr(), row.data_ptr(), x.shape[0], x.shape[1], _dtype_code(x), _stream()), "add_bias")
+    return x
+
+
+def scale_(x: torch.Tensor, scale: float) -> torch.Tensor:
+    """``x *= scale`` in place for an fp32 tensor."""
+    _need(x, "x", torch.float32)
+    _done(_lib().oxr_scale_f32(x.data_ptr(), float(scale), x.numel(), _stream()), "scale")
+    return x
+
+
+# --------------------------------------------------------------------------------------------------- matrix memory (mLSTM)
+def mlstm_scan(proj: torch.Tensor, q_col0: int, k_col0: int, v_col0: int, gates: torch.Tensor, gate_bias: torch.Tensor, *, heads: int, key_dim: int,
+               value_dim: int, cap: float, q_scale: float, state: torch.Tensor, cu_q: torch.Tensor, state_slots: torch.Tensor, n_requests: int
+               ) -> torch.Tensor:
+    """The matrix-memory recurrence over a packed step: fp32 ``o [tokens, heads * value_dim]`` (before the per-head norm). ``proj`` holds q, k and
+    v head by head from the given columns; ``gates [tokens, 2 * heads]`` (fp32) the input- and forget-gate projections, ``gate_bias [2 * heads]``
+    their biases; ``state`` (fp32, first axis the slot: S ``[heads, key_dim, value_dim]``, n ``[heads, key_dim]``, m ``[heads]``) is read and left at
+    the state after each request's last token."""
+    _need(proj, "proj")
+    _need(gates, "gates", torch.float32)
+    _need(gate_bias, "gate_bias", torch.float32)
+    if state.dtype != torch.float32 or state.stride(-1) != 1 or state[0].numel() < heads * key_dim * (value_dim + 1) + heads:
+        raise KernelError("mlstm_scan: the state must be fp32 rows of heads x (key_dim x value_dim + key_dim + 1)")
+    n = proj.shape[0]
+    if gates.shape != (n, 2 * heads) or gate_bias.numel() != 2 * heads:
+        raise KernelError("mlstm_scan: gates must be [tokens, 2 * heads] with one bias each")
+    y = torch.empty((n, heads * value_dim), dtype=torch.float32, device=proj.device)
+    _done(_lib().oxr_mlstm_scan(y.data_ptr(), proj.data_ptr(), n_requests, proj.shape[1], q_col0, k_col0, v_col0, gates.data_ptr(), gate_bias.data_ptr(),
+                                heads, key_dim, value_dim, float(cap), float(q_scale), state.data_ptr(), state.stride(0), cu_q.data_ptr(),
+                                state_slots.data_ptr(), _dtype_code(proj), _stream()), "mlstm_scan")
+    return y
+
+
+def head_norm_gate(y: torch.Tensor, proj: torch.Tensor, gate_col0: int, weight: torch.Tensor, heads: int, eps: float) -> torch.Tensor:
+    """``y [tokens, heads * d]`` (fp32): every head's stretch divided by its own root mean square, times ``weight``, times the sigmoid of the columns
+    ``[gate_col0, gate_col0 + heads * d)`` of ``proj``; rounded to ``proj.dtype``."""
+    _need(y, "y", torch.float32)
+    _need(proj, "proj")
+    _need(weight, "weight", torch.float32)
+    n, inner = y.shape
+    if inner % heads or weight.numel() != inner or gate_col0 + inner > proj.shape[1]:
+        raise KernelError("head_norm_gate: sizes do not fit")
+    out = torch.empty((n, inner), dtype=proj.dtype, device=y.device)
+    _done(_lib().oxr_head_norm_gate(out.data_ptr(), y.data_ptr(), proj.data_ptr(), n, proj.shape[1], gate_col0, weight.data_ptr(), heads, inner // heads,
+                                    float(eps), _dtype_code(proj), _stream()), "head_norm_gate")
+    return out
+
+
+# --------------------------------------------------------------------------------------------------- routed experts
+def route(z: torch.Tensor, *, top: int, groups: int, keep: int, scale: float) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Router logits ``z [tokens, E]`` (fp32) to the choice of ``top`` experts per token: scores are ``sigmoid(z)``; of ``groups`` equal groups of
+    neighbouring experts only the ``keep`` with the largest sum of their two best scores may be chosen from; the weights are the chosen scores
+    over their sum, times ``scale``. Returns ``gate [tokens, E]`` (fp32: a chosen expert's weight, else 0), ``ids [tokens, top]`` (int32) and
+    ``weights [tokens, top]`` (fp32)."""
+    _need(z, "z", torch.float32)
+    n, E = z.shape
+    gate = torch.empty((n, E), dtype=torch.float32, device=z.device)
+    ids = torch.empty((n, top), dtype=torch.int32, device=z.device)
+    wts = torch.empty((n, top), dtype=torch.float32, device=z.device)
+    _done(_lib().oxr_route(gate.data_ptr(), ids.data_ptr(), wts.data_ptr(), z.data_ptr(), n, E, int(top), int(groups), int(keep), float(scale), _stream()),
+          "route")
+    return gate, ids, wts
+
+
+def gated_relu2(u: torch.Tensor, gate: torch.Tensor, ff: int) -> torch.Tensor:
+    """``a[t, c] = gate[t, c // ff] * relu(u[t, c])^2`` for the stacked up-projections ``u [tokens, E * ff]`` of all experts."""
+    _need(u, "u")
+    _need(gate, "gate", torch.float32)
+    n, cols = u.shape
+    E = gate.shape[1]
+    if cols != E * ff or gate.shape[0] != n:
+        raise KernelError("gated_relu2: sizes do not fit")
+    a = torch.empty_like(u)
+    _done(_lib().oxr_gated_relu2(a.data_ptr(), u.data_ptr(), gate.data_ptr(), n, E, int(ff), _dtype_code(u), _stream()), "gated_relu2")
+    return a

@@ -6,8 +6,8 @@ Families and what each must provide:
   fp32 residual stream is part of the norm (oxr_runtime/language.py:94-99).
 * **PositionEncoding** – ``tables()``: whatever its mixers consume (rotary: fp32 cos and sin by position).
 * **Mixer** – ``forward(h, ctx, cache) -> y`` over the step's packed tokens; ``cache_need()`` says what it keeps
-  between steps: paged keys/values (:class:`PagedKVNeed`), fixed-size per-request state (:class:`StateNeed`),
-  or nothing. ``tile_specs()`` (optional) asks the batch builder for tile lists.
+  between steps: paged keys/values (:class:`PagedKVNeed`), fixed-size per-request state (:class:`StateNeed`), both
+  (a pair), or nothing. ``tile_specs()`` (optional) asks the batch builder for tile lists.
 * **FeedForward** – ``forward(h) -> y``.
 * **Block arrangement** – puts a mixer and a feed-forward behind their norms.
 * **Embedding** – ``forward(ids) -> x``; **Head** – ``forward(h) -> fp32 logits`` (it is handed the embedding part).
@@ -212,7 +212,8 @@ class Mixer(Part):
     """Whether ``forward`` may be handed a lazily normalised ``h`` (it then passes ``h`` to its first projection and
     does nothing else with it)."""
 
-    def cache_need(self) -> PagedKVNeed | StateNeed | None:
+    def cache_need(self) -> "PagedKVNeed | StateNeed | tuple[PagedKVNeed, StateNeed] | None":
+        """What the mixer keeps between steps: pages of keys and values, a fixed-size state per request, both (a pair), or nothing."""
         return None
 
     def tile_specs(self) -> list[tuple[int, int, int]]:

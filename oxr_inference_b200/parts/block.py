@@ -9,7 +9,8 @@ from oxr_inference_b200.parts.base import ARRANGEMENTS, DeferredLinear, FeedForw
 
 @ARRANGEMENTS.register("pre_norm")
 class PreNormBlock:
-    """``x += mixer(norm1(x)); x += feed_forward(norm2(x))``, carried as (last output not yet added, residual):
+    """``x += mixer(norm1(x)); x += feed_forward(norm2(x))`` (the second sublayer only when the block has a feed-forward), carried as
+    (last output not yet added, residual):
     each norm first adds the pending output into the fp32 residual stream (oxr_runtime/language.py:184-187,
     253-257,266-269). Returns the feed-forward's output and the residual; whoever comes next adds them.
 
@@ -22,13 +23,17 @@ class PreNormBlock:
 
     supports_deferred = True
 
-    def __init__(self, mixer: Mixer, mixer_norm: Norm, feed_forward: FeedForward, feed_forward_norm: Norm):
+    def __init__(self, mixer: Mixer, mixer_norm: Norm, feed_forward: FeedForward | None, feed_forward_norm: Norm | None):
+        if (feed_forward is None) != (feed_forward_norm is None):
+            raise ValueError("a feed-forward comes with its norm or not at all")
         self.mixer, self.mixer_norm = mixer, mixer_norm
         self.feed_forward, self.feed_forward_norm = feed_forward, feed_forward_norm
 
     def parts(self) -> dict[str, object]:
-        return {"mixer": self.mixer, "mixer_norm": self.mixer_norm, "feed_forward": self.feed_forward,
-                "feed_forward_norm": self.feed_forward_norm}
+        out = {"mixer": self.mixer, "mixer_norm": self.mixer_norm}
+        if self.feed_forward is not None:
+            out.update(feed_forward=self.feed_forward, feed_forward_norm=self.feed_forward_norm)
+        return out
 
     @property
     def accepts_deferred_input(self) -> bool:
@@ -43,7 +48,17 @@ class PreNormBlock:
         return norm.forward(x, residual)
 
     def forward(self, x, residual: torch.Tensor | None, ctx: StepContext, cache: LayerCache, defer_output: bool = False):
-        h, residual = self._norm(self.mixer_norm, x, residual, self.mixer)
+        if residual is None and torch.is_tensor(x) and x.dtype == torch.float32 and getattr(self.mixer_norm, "runtime", None) is not None \
+                and self.mixer_norm.runtime.dtype != torch.float32 and hasattr(self.mixer_norm, "stream_norm"):
+            # the embedding handed over the fp32 stream itself (not 16-bit activations): it is the residual, nothing is pending
+            h, residual = self.mixer_norm.stream_norm(x), x
+        elif x is None:
+            # the block before kept the stream whole
+            h = self.mixer_norm.stream_norm(residual)
+        else:
+            h, residual = self._norm(self.mixer_norm, x, residual, self.mixer)
+        if self.feed_forward is None:   # the mixer's sublayer only: its output stays pending for whoever comes next
+            return self.mixer.forward(h, ctx, cache), residual
         if self.feed_forward_norm.accepts_deferred:
             a = self.mixer.forward_deferred(h, ctx, cache)
         else:

@@ -40,11 +40,11 @@ class TokenEmbedding(Embedding):
 @HEADS.register("linear_head")
 class OutputHead(Head):
     """``logits = h W^T`` in fp32 (oxr_runtime/language.py:158,213-214). ``tied``: W is the embedding table, which
-    the reference does not offer (its head is always a tensor of its own)."""
+    the reference does not offer (its head is always a tensor of its own). ``scale``: the fp32 logits are multiplied by it."""
 
-    def __init__(self, runtime: Runtime, embedding: Embedding, *, vocab_size: int, hidden_size: int, tied: bool):
+    def __init__(self, runtime: Runtime, embedding: Embedding, *, vocab_size: int, hidden_size: int, tied: bool, scale: float = 1.0):
         self.runtime, self.embedding = runtime, embedding
-        self.vocab, self.hidden, self.tied = int(vocab_size), int(hidden_size), bool(tied)
+        self.vocab, self.hidden, self.tied, self.scale = int(vocab_size), int(hidden_size), bool(tied), float(scale)
         self.weight: torch.Tensor | None = None
 
     def parameters(self) -> dict[str, ParamInfo]:
@@ -58,7 +58,8 @@ class OutputHead(Head):
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         w = self.embedding.weight if self.tied else self.weight
-        return ops.linear(h, w, torch.float32)
+        logits = ops.linear(h, w, torch.float32)
+        return logits if self.scale == 1.0 else ops.scale_(logits, self.scale)
 
 
 class DecoderModel:

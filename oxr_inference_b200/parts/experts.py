@@ -1,0 +1,72 @@
+"""A feed-forward of routed experts: each token runs a few of many small feed-forward layers, chosen by a router."""
+
+from __future__ import annotations
+
+import torch
+
+from oxr_inference_b200 import ops
+from oxr_inference_b200.parts.base import FEED_FORWARDS, FeedForward, ParamInfo, Runtime
+
+
+@FEED_FORWARDS.register("routed_experts")
+class RoutedExperts(FeedForward):
+    """``experts`` feed-forward layers ``e<i>``: ``down_i( relu(up_i h)^2 )``, no biases. The router's logits ``z = W_router h`` are computed
+    in fp32; scores ``s = sigmoid(z)``. The experts form ``groups`` equal groups of neighbours; a group's score is the sum of its two
+    largest scores, and only experts of the ``keep`` best groups can be chosen. Each token runs the ``top`` allowed experts with the
+    largest scores; their outputs are added with weights ``s / (sum of the chosen s + 1e-20) * scale``.
+
+    All experts' up-projections are stacked into one matrix ``[experts * ff, hidden]`` and their down-projections side by side into
+    ``[hidden, experts * ff]``, so the layer is two products for any batch: the activation kernel multiplies each expert's stretch of
+    columns by the token's weight for that expert (zero when it was not chosen), and the sum over experts happens inside the second
+    product's reduction. A token's result does not depend on what else is in the batch."""
+
+    def __init__(self, runtime: Runtime, *, hidden_size: int, intermediate_size: int, experts: int, top: int, groups: int = 1, keep: int = 1,
+                 scale: float = 1.0):
+        self.runtime = runtime
+        self.hidden, self.ff, self.E, self.top = int(hidden_size), int(intermediate_size), int(experts), int(top)
+        self.groups, self.keep, self.scale = int(groups), int(keep), float(scale)
+        if self.groups < 1 or self.E % self.groups:
+            raise ValueError(f"{self.E} experts do not form {self.groups} equal groups")
+        if not 1 <= self.keep <= self.groups:
+            raise ValueError(f"{self.keep} of {self.groups} groups cannot be kept")
+        if not 1 <= self.top <= self.keep * (self.E // self.groups):
+            raise ValueError(f"{self.top} experts cannot be chosen from {self.keep} groups of {self.E // self.groups}")
+        self.up: torch.Tensor | None = None       # [E * ff, hidden]
+        self.down: torch.Tensor | None = None     # [hidden, E * ff]
+        self.router: torch.Tensor | None = None   # [E, hidden]
+
+    def parameters(self) -> dict[str, ParamInfo]:
+        out = {"router": ParamInfo((self.E, self.hidden))}
+        for e in range(self.E):
+            out[f"e{e}.up"] = ParamInfo((self.ff, self.hidden))
+            out[f"e{e}.down"] = ParamInfo((self.hidden, self.ff))
+        return out
+
+    def _stack(self, have: torch.Tensor | None, shape: tuple[int, int], dtype: torch.dtype) -> torch.Tensor:
+        if have is None:
+            return torch.empty(shape, dtype=dtype, device=self.runtime.device)
+        # one expert stored in 32-bit: the whole stack is then kept and multiplied in 32-bit
+        return have.float() if dtype == torch.float32 and have.dtype != torch.float32 else have
+
+    def assign(self, name: str, tensor: torch.Tensor) -> None:
+        infos = self.parameters()
+        if name not in infos:
+            raise KeyError(name)
+        dtype = self.runtime.store_dtype(infos[name], tensor.dtype)
+        if name == "router":
+            self.router = tensor.to(device=self.runtime.device, dtype=dtype).contiguous()
+            return
+        expert, which = name.split(".")
+        e = int(expert[1:])
+        if which == "up":
+            self.up = self._stack(self.up, (self.E * self.ff, self.hidden), dtype)
+            self.up[e * self.ff:(e + 1) * self.ff].copy_(tensor)
+        else:
+            self.down = self._stack(self.down, (self.hidden, self.E * self.ff), dtype)
+            self.down[:, e * self.ff:(e + 1) * self.ff].copy_(tensor)
+
+    def forward(self, h: torch.Tensor) -> torch.Tensor:
+        z = ops.linear(h, self.router, torch.float32)
+        gate, _, _ = ops.route(z, top=self.top, groups=self.groups, keep=self.keep, scale=self.scale)
+        u = ops.linear(h, self.up)
+        return ops.linear(ops.gated_relu2(u, gate, self.ff), self.down)

@@ -8,7 +8,7 @@ import math
 import torch
 
 from oxr_inference_b200 import ops
-from oxr_inference_b200.parts.base import MIXERS, LayerCache, Mixer, PagedKVNeed, ParamInfo, PositionEncoding, Runtime, StepContext
+from oxr_inference_b200.parts.base import MIXERS, LayerCache, Mixer, PagedKVNeed, ParamInfo, PositionEncoding, Runtime, StateNeed, StepContext
 from oxr_inference_b200.parts.linear import StackedLinear
 
 
@@ -37,31 +37,73 @@ def bias_by_distance(table: torch.Tensor, far: float) -> torch.Tensor:
 
 @MIXERS.register("masked_attention")
 class MaskedAttention(Mixer):
-    """``q, k, v = h W^T`` (no biases, no rotation) -> K and V into the paged cache -> softmax attention of each new token over the
-    keys it sees -> ``W_o``. Query head h reads key/value head ``h // (heads / kv_heads)``; keys have ``key_dim`` entries, values
+    """``q, k, v = h W^T`` (no rotation) -> K and V into the paged cache -> softmax attention of each new token over the keys it
+    sees -> ``W_o``. Query head h reads key/value head ``h // (heads / kv_heads)``; keys have ``key_dim`` entries, values
     ``value_dim``. ``chunk`` > 0: position i sees j <= i only inside its own chunk of that many positions, counted from 0 (not from
     where a prompt was cut). ``window`` > 0: only the last ``window`` keys. ``bias_rows`` > 0: a learned table ``rel [bias_rows, heads]``
-    is added to the scaled score by bucketed distance (:func:`distance_bucket`, ``bias_far``)."""
+    is added to the scaled score by bucketed distance (:func:`distance_bucket`, ``bias_far``).
+
+    Optional, between the projection and the cache: ``biases`` (tensors ``q.b``, ``k.b``, ``v.b`` added to the projections and ``o.b`` to
+    the output); ``conv_taps`` > 0: every channel of q, k and v passes a causal filter over time (``q.conv`` ... ``[channels, taps]``, the
+    last tap on the current token, zeros before a sequence's start; the last ``taps - 1`` projected values of each request are kept in a
+    state slot); ``temp_every`` > 0: the query at position p is multiplied by ``1 + temp_coef ln(floor((p + 1) / temp_every) + 1)``;
+    ``value_mix``: ``"keep"`` leaves this layer's values in the step's shared dictionary under ``value_mix_key``, ``"blend"`` replaces its own
+    by ``(1 - vmix) v + vmix kept`` (a learned number ``vmix``; the blended values are what the cache holds). Both kinds own a ``vmix``
+    tensor; the keeping layer does not use its one."""
 
     def __init__(self, runtime: Runtime, position: PositionEncoding | None, *, hidden_size: int, num_heads: int, num_kv_heads: int, key_dim: int,
-                 value_dim: int, scale: float, chunk: int = 0, window: int = 0, bias_rows: int = 0, bias_far: float = 0.0):
+                 value_dim: int, scale: float, chunk: int = 0, window: int = 0, bias_rows: int = 0, bias_far: float = 0.0, biases: bool = False,
+                 conv_taps: int = 0, temp_coef: float = 0.0, temp_every: int = 0, value_mix: str | None = None,
+                 value_mix_key: str = "kept_values"):
         if position is not None:
             raise ValueError("masked_attention takes no position encoding: positions enter through its mask and bias")
         if num_heads % num_kv_heads:
             raise ValueError(f"{num_heads} heads are not a multiple of {num_kv_heads} KV heads")
+        if value_mix not in (None, "keep", "blend"):
+            raise ValueError(f"value_mix {value_mix!r} is not one of None, 'keep', 'blend'")
         self.runtime = runtime
         self.hidden, self.H, self.KV, self.DK, self.DV = int(hidden_size), int(num_heads), int(num_kv_heads), int(key_dim), int(value_dim)
         self.scale, self.chunk, self.window = float(scale), int(chunk), int(window)
         self.bias_rows, self.bias_far = int(bias_rows), float(bias_far)
-        self.qkv = StackedLinear(runtime, self.hidden, {"q": self.H * self.DK, "k": self.KV * self.DK, "v": self.KV * self.DV})
+        self.biases, self.taps = bool(biases), int(conv_taps)
+        self.temp_coef, self.temp_every = float(temp_coef), int(temp_every)
+        self.value_mix, self.value_mix_key = value_mix, str(value_mix_key)
+        self.cq, self.ck, self.cv = self.H * self.DK, self.KV * self.DK, self.KV * self.DV
+        self.qkv = StackedLinear(runtime, self.hidden, {"q": self.cq, "k": self.ck, "v": self.cv})
         self.out = StackedLinear(runtime, self.H * self.DV, {"o": self.hidden})
         self.rel: torch.Tensor | None = None
         self.dist_bias: torch.Tensor | None = None
+        self.vectors: dict[str, torch.Tensor] = {}
+        self.qkv_bias: torch.Tensor | None = None
+        self.qkv_conv: torch.Tensor | None = None
+
+    @property
+    def between(self) -> bool:
+        """Whether anything happens between the projection and the cache (then one kernel does all of it and the cache write)."""
+        return self.biases or self.taps > 0 or self.temp_every > 0 or self.value_mix is not None
+
+    @property
+    def plain(self) -> bool:
+        """Causal or windowed softmax over keys and values of one size: what the TMA / tcgen05 attention kernels take."""
+        return self.chunk == 0 and self.bias_rows == 0 and self.DK == self.DV
+
+    def _vector_shapes(self) -> dict[str, tuple[int, ...]]:
+        out: dict[str, tuple[int, ...]] = {}
+        sizes = {"q": self.cq, "k": self.ck, "v": self.cv}
+        if self.biases:
+            out.update({f"{n}.b": (c,) for n, c in sizes.items()})
+            out["o.b"] = (self.hidden,)
+        if self.taps > 0:
+            out.update({f"{n}.conv": (c, self.taps) for n, c in sizes.items()})
+        if self.value_mix is not None:
+            out["vmix"] = ()
+        return out
 
     def parameters(self) -> dict[str, ParamInfo]:
         out = {**self.qkv.parameters(), **self.out.parameters()}
         if self.bias_rows:
             out["rel"] = ParamInfo((self.bias_rows, self.H), role="vector")
+        out.update({name: ParamInfo(shape, role="vector") for name, shape in self._vector_shapes().items()})
         return out
 
     def assign(self, name: str, tensor: torch.Tensor) -> None:
@@ -71,15 +113,29 @@ class MaskedAttention(Mixer):
             self.out.assign(name, tensor)
         elif name == "rel" and self.bias_rows:
             self.rel = tensor.to(device=self.runtime.device, dtype=torch.float32).contiguous()
+        elif name in self._vector_shapes():
+            self.vectors[name] = tensor.to(device=self.runtime.device, dtype=torch.float32).contiguous()
         else:
             raise KeyError(name)
 
     def finish_loading(self) -> None:
         if self.rel is not None:
             self.dist_bias = bias_by_distance(self.rel, self.bias_far)
+        v = self.vectors
+        if self.biases:
+            self.qkv_bias = torch.cat([v["q.b"], v["k.b"], v["v.b"]]).contiguous()
+        if self.taps > 0:
+            self.qkv_conv = torch.cat([v["q.conv"], v["k.conv"], v["v.conv"]]).contiguous()
+        if self.value_mix is not None:
+            v["vmix"] = v["vmix"].reshape(1)
 
-    def cache_need(self) -> PagedKVNeed:
-        return PagedKVNeed(self.KV, self.DK, self.window, value_dim=self.DV, chunk=self.chunk)
+    def cache_need(self):
+        # keys and values of one size under a causal or windowed mask: the need of plain grouped-query attention, whose pools get TMA maps
+        paged = (PagedKVNeed(self.KV, self.DK, self.window) if self.plain else
+                 PagedKVNeed(self.KV, self.DK, self.window, value_dim=self.DV, chunk=self.chunk))
+        if self.taps > 1:
+            return paged, StateNeed(((self.cq + self.ck + self.cv) * (self.taps - 1),), torch.float32)
+        return paged
 
     @property
     def tiled(self) -> bool:
@@ -89,27 +145,55 @@ class MaskedAttention(Mixer):
         return (self.DK,) if self.tiled else ()
 
     def tile_specs(self) -> list[tuple[int, int, int]]:
-        return ops.attention_tile_specs(self.H, self.KV, self.DK, self.runtime.dtype) if self.tiled else []
+        if not self.tiled:
+            return []
+        return ops.attention_tile_specs(self.H, self.KV, self.DK, self.runtime.dtype, self.runtime.page_size if self.plain else None)
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
+        y = self.out(self._attend(h, ctx, cache))
+        if self.biases:
+            ops.add_bias_(y, self.vectors["o.b"])
+        return y
+
+    def _attend(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         group = cache.group
         k_pool, v_pool = group.k_pool[cache.layer_in_group], group.v_pool[cache.layer_in_group]
         qkv = self.qkv(h)
         if qkv.dtype != k_pool.dtype:
             qkv = ops.cast(qkv, k_pool.dtype)
-        if cache.store:
-            ops.scatter_rows(k_pool, qkv, self.H * self.DK, group.slots, ctx.status, pool2=v_pool)   # the k columns, then the v columns
-        if self.tiled and qkv.dtype == torch.bfloat16:
+        if self.between:
+            blend = first = None
+            if self.value_mix == "blend":
+                if self.value_mix_key not in ctx.shared:
+                    raise ValueError(f"no layer before this one kept its values under {self.value_mix_key!r}")
+                blend, first = self.vectors["vmix"], ctx.shared[self.value_mix_key]
+            q, kept = ops.conv_qkv_store(
+                qkv, self.cq, self.ck, self.cv, conv=self.qkv_conv, bias=self.qkv_bias, tails=cache.state, k_pool=k_pool, v_pool=v_pool,
+                slots=group.slots if cache.store else ctx.no_store_slots, req_of_token=ctx.req_of_token, cu_q=ctx.cu_q,
+                state_slots=ctx.state_slots, positions=ctx.positions, n_requests=ctx.n_requests, status=ctx.status, temp_coef=self.temp_coef,
+                temp_every=self.temp_every, blend=blend, first=first, keep_values=self.value_mix == "keep")
+            if self.value_mix == "keep":
+                ctx.shared[self.value_mix_key] = kept
+            q_width = self.cq
+        else:
+            if cache.store:
+                ops.scatter_rows(k_pool, qkv, self.cq, group.slots, ctx.status, pool2=v_pool)   # the k columns, then the v columns
+            q, q_width = qkv, qkv.shape[1]
+        if self.tiled and q.dtype == torch.bfloat16:
             # keys and values of one size the tiled kernels are built for: tensor cores, split-KV for single tokens
-            q = qkv[:, :self.H * self.DK].contiguous().view(ctx.n_tokens, self.H, self.DK)
-            o = ops.paged_attention(q, k_pool, v_pool, tiles=ctx.tiles, cu_q=ctx.cu_q, ctx_lens=ctx.ctx_lens, block_table=group.block_table,
-                                    page_size=group.page_size, scale=self.scale, window=self.window, kv_len_bound=ctx.kv_len_bound,
-                                    status=ctx.status, chunk=self.chunk, dist_bias=self.dist_bias)
-            return self.out(o.view(ctx.n_tokens, self.H * self.DV))
-        o = ops.attention_rows(qkv, self.H, k_pool, v_pool, value_dim=self.DV, positions=ctx.positions, req_of_token=ctx.req_of_token,
-                               block_table=group.block_table, scale=self.scale, chunk=self.chunk, window=self.window,
-                               dist_bias=self.dist_bias, status=ctx.status)
-        return self.out(o)
+            q = (q if q_width == self.cq else q[:, :self.cq].contiguous()).view(ctx.n_tokens, self.H, self.DK)
+            if self.plain:
+                o = ops.paged_attention(q, k_pool, v_pool, tiles=ctx.tiles, cu_q=ctx.cu_q, ctx_lens=ctx.ctx_lens, block_table=group.block_table,
+                                        page_size=group.page_size, scale=self.scale, window=self.window, kv_len_bound=ctx.kv_len_bound,
+                                        status=ctx.status, kv_maps=group.kv_maps, layer_in_pool=cache.layer_in_group, uneven=ctx.uneven)
+            else:
+                o = ops.paged_attention(q, k_pool, v_pool, tiles=ctx.tiles, cu_q=ctx.cu_q, ctx_lens=ctx.ctx_lens, block_table=group.block_table,
+                                        page_size=group.page_size, scale=self.scale, window=self.window, kv_len_bound=ctx.kv_len_bound,
+                                        status=ctx.status, chunk=self.chunk, dist_bias=self.dist_bias)
+            return o.view(ctx.n_tokens, self.H * self.DV)
+        return ops.attention_rows(q, self.H, k_pool, v_pool, value_dim=self.DV, positions=ctx.positions, req_of_token=ctx.req_of_token,
+                                  block_table=group.block_table, scale=self.scale, chunk=self.chunk, window=self.window,
+                                  dist_bias=self.dist_bias, status=ctx.status)
 
 
 @MIXERS.register("latent_attention")
