@@ -435,6 +435,181 @@ def radapel_workload(args) -> int:
     return 0
 
 
+def bifusun_config(width: int, ff: int, heads: int, kv_heads: int, head_dim: int, layers: int, vocab: int, experts: int = 16, top: int = 4) -> dict:
+    """A Bifusun model of a real model's layer sizes: a matrix-memory layer, then three attention layers (biases, a filter of four taps, a
+    query temperature, blended values), in turn; each with a feed-forward of ``experts`` experts of which a token runs ``top``, whose
+    ``top`` experts together are as wide as the dense feed-forward of the Qwen3 model beside it."""
+    moe = {"kind": "moe", "expert": {"ff": ff // top}, "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": 4, "keep": 3}}}
+    attention = {"type": "attention", "mlp": moe, "mixer": {
+        "heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "conv": 4,
+        "q_temp": {"coef": 0.5, "every": 128}, "v_mix": True}}
+    mlstm = {"type": "mlstm", "mlp": moe, "mixer": {"heads": 8, "dim": width // 16, "vdim": width // 8, "gate_cap": 15.0}}
+    turn = [mlstm, attention, attention, attention]
+    return {"architecture": "Bifusun", "embedding": {"scale": 1.0}, "logit_scale": 1.0, "norm": {"eps": 1e-6}, "vocab": vocab, "width": width,
+            "layers": [turn[i % 4] for i in range(layers)]}
+
+
+def bifusun_kernels(width: int, heads: int, kv_heads: int, head_dim: int, ff: int, experts: int = 16, top: int = 4) -> list[dict]:
+    """Each kernel of the design alone, at one model size, beside the like kernel of the paths that were there before: device time
+    (median, L2 flushed between calls), the bytes or FLOPs it has to move or do, and the fraction of the measured peak."""
+    import torch
+
+    from oxr_inference_b200 import ops
+
+    dev = "cuda"
+    hbm_gbs, bf16_tflops, _ = peaks()
+    flush = torch.zeros(128 << 20, dtype=torch.float32, device=dev)
+    status = ops.new_status(dev)
+    bf = torch.bfloat16
+    rows = []
+
+    def put(name, like, ms, *, bytes_=None, flops=None):
+        row = {"kernel": name, "like": like, "us": round(ms * 1e3, 1)}
+        if bytes_ is not None:
+            row.update(gb_s=round(bytes_ / (ms * 1e-3) / 1e9, 1), frac=round(bytes_ / (ms * 1e-3) / 1e9 / hbm_gbs, 4), bound="hbm")
+        else:
+            row.update(tflop_s=round(flops / (ms * 1e-3) / 1e12, 2), frac=round(flops / (ms * 1e-3) / 1e12 / bf16_tflops, 4), bound="tensor")
+        rows.append(row)
+
+    P, T, B, CTX = 16, 2048, 8, 2048
+    H, KV, D = heads, kv_heads, head_dim
+    g = torch.Generator(device=dev).manual_seed(0)
+
+    def rand(*shape, dtype=bf, scale=1.0):
+        return (torch.randn(*shape, generator=g, device=dev) * scale).to(dtype)
+
+    def i32(x):
+        return torch.tensor(x, dtype=torch.int32, device=dev)
+
+    n_pages = B * (CTX // P) + T // P + 8
+    k_pool, v_pool = rand(n_pages, P, KV, D), rand(n_pages, P, KV, D)
+    cq, ck, cv = H * D, KV * D, KV * D
+    C = cq + ck + cv
+    taps = 4
+    conv, bias = rand(C, taps, dtype=torch.float32), rand(C, dtype=torch.float32)
+    cos = torch.ones(8192, D // 2, device=dev)
+    ones = torch.ones(D, device=dev)
+    tails = torch.zeros(B + 1, C * (taps - 1), device=dev)
+    lam = torch.tensor([0.3], device=dev)
+    for name, q_lens in (("prefill 2048", [T]), ("decode b8", [1] * B)):
+        n = sum(q_lens)
+        qkv = rand(n, C, scale=0.5)
+        first = rand(n, cv)
+        cu = i32([0] + list(torch.tensor(q_lens).cumsum(0)))
+        req = torch.repeat_interleave(torch.arange(len(q_lens), dtype=torch.int32), torch.tensor(q_lens)).to(dev)
+        pos = i32(list(range(T)) if len(q_lens) == 1 else [CTX - 1] * B)
+        slots = i32([(r * (CTX // P)) * P + (i if len(q_lens) == 1 else CTX - 1) for r, x in enumerate(q_lens) for i in range(x)])
+        ms = _time_ms(lambda: ops.qk_norm_rope_store(qkv, ones, ones, cos, cos, pos, slots, k_pool, v_pool, H, KV, D, 1e-6, status), flush=flush)
+        put(f"qk_norm_rope_store {name}", None, ms, bytes_=n * C * 2 * 2)
+        ms = _time_ms(lambda: ops.conv_qkv_store(qkv, cq, ck, cv, conv=conv, bias=bias, tails=tails, k_pool=k_pool, v_pool=v_pool, slots=slots,
+                                                 req_of_token=req, cu_q=cu, state_slots=i32(list(range(len(q_lens)))), positions=pos,
+                                                 n_requests=len(q_lens), status=status, temp_coef=0.5, temp_every=128, blend=lam, first=first),
+                      flush=flush)
+        put(f"conv_qkv_store {name} (bias, 4 taps, temperature, blend, cache write, tail roll)", f"qk_norm_rope_store {name}", ms,
+            bytes_=n * (C * 2 * 2 + cv * 2) + len(q_lens) * C * (taps - 1) * 8)
+
+    # ---- matrix memory: 8 heads, keys of width / 16, values of width / 8; beside the Mamba-2 scan of the same inner width
+    MH, DK, DV = 8, width // 16, width // 8
+    inner = MH * DV
+    size = MH * DK * DV + MH * DK + MH
+    state = torch.zeros(B + 1, size, device=dev)
+    gate_bias = rand(2 * MH, dtype=torch.float32)
+    norm_w = torch.ones(inner, device=dev)
+    SH, SP, SN, SG = inner // 64, 64, 128, 8
+    s_channels = inner + 2 * SG * SN
+    ssm = torch.zeros(B + 1, SH * SP * SN, device=dev)
+    vec = {k: rand(*shape, dtype=torch.float32, scale=0.1) for k, shape in (("dt_bias", (SH,)), ("A_log", (SH,)), ("D", (SH,)))}
+    for name, q_lens in (("prefill 2048", [T]), ("decode b8", [1] * B)):
+        n = sum(q_lens)
+        proj = rand(n, 2 * MH * DK + 2 * inner, scale=0.5)
+        gates = torch.randn(n, 2 * MH, device=dev)
+        cu = i32([0] + list(torch.tensor(q_lens).cumsum(0)))
+        common = dict(cu_q=cu, state_slots=i32(list(range(len(q_lens)))), n_requests=len(q_lens))
+        xbc, sproj = rand(n, s_channels, scale=0.5), rand(n, 2 * inner + 2 * SG * SN + SH, scale=0.5)
+        ms = _time_ms(lambda: ops.mamba_scan(xbc, sproj, inner + s_channels, heads=SH, vdim=SP, state=SN, groups=SG, dt_bias=vec["dt_bias"],
+                                             a_log=vec["A_log"], d_skip=vec["D"], ssm=ssm, **common), flush=flush)
+        put(f"mamba_scan {name}", None, ms, bytes_=n * (s_channels * 2 + inner * 4) + len(q_lens) * SH * SP * SN * 8)
+        ms = _time_ms(lambda: ops.mlstm_scan(proj, 0, MH * DK, 2 * MH * DK, gates, gate_bias, heads=MH, key_dim=DK, value_dim=DV, cap=15.0,
+                                             q_scale=DK ** -0.5, state=state, **common), flush=flush)
+        put(f"mlstm_scan {name}", f"mamba_scan {name}", ms, bytes_=n * ((2 * MH * DK + inner) * 2 + inner * 4) + len(q_lens) * size * 8)
+        y = torch.randn(n, inner, device=dev)
+        ms = _time_ms(lambda: ops.gated_group_norm(y, proj, 0, norm_w, 8, 1e-6), flush=flush)
+        put(f"gated_group_norm {name}", None, ms, bytes_=n * inner * (4 + 2 + 2))
+        ms = _time_ms(lambda: ops.head_norm_gate(y, proj, 2 * MH * DK + inner, norm_w, MH, 1e-6), flush=flush)
+        put(f"head_norm_gate {name}", f"gated_group_norm {name}", ms, bytes_=n * inner * (4 + 2 + 2))
+
+    # ---- the feed-forward: router, activation, and the layer as a whole beside the dense gated one of equal active width
+    E, ffe = experts, ff // top
+    router_w, up_w, down_w = rand(E, width, scale=0.02), rand(E * ffe, width, scale=0.02), rand(width, E * ffe, scale=0.02)
+    gate_up_w, dense_down_w = rand(2 * ff, width, scale=0.02), rand(width, ff, scale=0.02)
+    from oxr_inference_b200.parts.base import Runtime
+    from oxr_inference_b200.parts.experts import RoutedExperts
+
+    part = RoutedExperts(Runtime(device=torch.device(dev), dtype=bf, max_positions=1, status=status), hidden_size=width, intermediate_size=ffe,
+                         experts=E, top=top, groups=4, keep=3, scale=2.5)
+    part.router, part.up, part.down = router_w, up_w, down_w
+    part.finish_loading()
+    for n in (T, B):
+        h = rand(n, width)
+        z = torch.randn(n, E, device=dev)
+        ms = _time_ms(lambda: ops.route(z, top=top, groups=4, keep=3, scale=2.5), flush=flush)
+        put(f"route {n} rows", None, ms, bytes_=n * (E * 8 + top * 8))
+        gu = rand(n, 2 * ff)
+        ms = _time_ms(lambda: ops.silu_mul(gu), flush=flush)
+        put(f"silu_mul {n} rows", None, ms, bytes_=n * ff * 6)
+        u = rand(n, E * ffe)
+        gate = ops.route(z, top=top, groups=4, keep=3, scale=2.5)[0]
+        ms = _time_ms(lambda: ops.gated_relu2(u, gate, ffe), flush=flush)
+        put(f"gated_relu2 {n} rows (all {E} experts' columns)", f"silu_mul {n} rows", ms, bytes_=n * E * ffe * 4)
+        ms = _time_ms(lambda: ops.linear(ops.silu_mul(ops.linear(h, gate_up_w)), dense_down_w), flush=flush)
+        dense_flops, dense_bytes = 2 * n * width * 3 * ff, 3 * ff * width * 2
+        moe_flops = 2 * n * width * 2 * ff     # the chosen experts only
+        touched = E * (1 - (1 - top / E) ** n)
+        moe_bytes = 2 * touched * ffe * width * 2
+        if n >= 256:
+            put(f"dense gated feed-forward {n} rows (three products of {ff})", None, ms, flops=dense_flops)
+        else:
+            put(f"dense gated feed-forward {n} rows (three products of {ff})", None, ms, bytes_=dense_bytes)
+        ms = _time_ms(lambda: part.forward(h), flush=flush)
+        if n >= 256:
+            put(f"routed experts {n} rows ({top} of {E} experts of {ffe}; FLOPs of the chosen experts)", f"dense gated feed-forward {n} rows (three products of {ff})", ms,
+                flops=moe_flops)
+        else:
+            put(f"routed experts {n} rows ({top} of {E} experts of {ffe}; bytes of the experts touched)", f"dense gated feed-forward {n} rows (three products of {ff})", ms,
+                bytes_=moe_bytes)
+    ops.check_status(status)
+    return rows
+
+
+def bifusun_workload(args) -> int:
+    """The Bifusun design beside Qwen3 at equal sizes: whole-model prefill and decode throughput at two sizes, and every kernel of the new
+    parts against its roofline beside the like kernel of the paths that were there before."""
+    import torch
+
+    sizes = [("2048 wide, 8 layers", dict(width=2048, ff=8192, heads=16, kv_heads=4, head_dim=128, layers=8, vocab=32768)),
+             ("4096 wide, 8 layers (Qwen3-8B layer sizes)", dict(width=4096, ff=12288, heads=32, kv_heads=8, head_dim=128, layers=8, vocab=32768))]
+    K, W = args.steps, max(args.warmup, 3)
+    sampler = ClockSampler()
+    sampler.start()
+    out = {"workload": "bifusun", "dtype": "bf16", "data": "synthetic uniform token ids, random weights N(0, 0.02)", "steps": K, "warmup": W,
+           "batch": 8, "context": args.context, "prefill_tokens": PREFILL_TOKENS, "peaks": peaks()[2], "sizes": []}
+    for name, s in sizes:
+        qwen = {"architectures": ["Qwen3ForCausalLM"], "model_type": "qwen3", "hidden_size": s["width"], "intermediate_size": s["ff"],
+                "num_hidden_layers": s["layers"], "num_attention_heads": s["heads"], "num_key_value_heads": s["kv_heads"], "head_dim": s["head_dim"],
+                "rms_norm_eps": 1e-6, "rope_theta": 1000000.0, "vocab_size": s["vocab"], "tie_word_embeddings": False,
+                "max_position_embeddings": 8192}
+        row = {"size": name}
+        for design, cfg in (("qwen3", qwen), ("bifusun", bifusun_config(**s))):
+            row[design] = design_throughput(cfg, s["vocab"], K, W, 8, args.context, PREFILL_TOKENS)
+            torch.cuda.empty_cache()
+        out["sizes"].append(row)
+    last = sizes[-1][1]
+    out["kernels"] = bifusun_kernels(last["width"], last["heads"], last["kv_heads"], last["head_dim"], last["ff"])
+    out["clocks"] = sampler.stop()
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -445,9 +620,9 @@ def main() -> int:
     ap.add_argument("--skip-points", action="store_true", help="leave out batch 1 and 64 and the further points (quick runs)")
     ap.add_argument("--skip-serving", action="store_true", help="leave the two serving workloads out of `points`")
     ap.add_argument("--context", type=int, default=CONTEXT, help="tokens each request holds when the decode steps are timed")
-    ap.add_argument("--workload", default="decode", choices=("decode", "continuous", "chunked", "radapel"),
+    ap.add_argument("--workload", default="decode", choices=("decode", "continuous", "chunked", "radapel", "bifusun"),
                     help="decode: the headline line (default); continuous / chunked: the two serving workloads, one line each; "
-                         "radapel: the Radapel design beside Qwen3 at equal sizes, whole models and kernel by kernel")
+                         "radapel / bifusun: that design beside Qwen3 at equal sizes, whole models and kernel by kernel")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"this engine runs on one GPU; --gpus {args.gpus} is not supported")
@@ -456,6 +631,8 @@ def main() -> int:
         return reference_arm(args)
     if args.workload == "radapel":
         return radapel_workload(args)
+    if args.workload == "bifusun":
+        return bifusun_workload(args)
     if args.workload != "decode":
         return serving_workload(args.workload)
     K, W = args.steps, max(args.warmup, 3)

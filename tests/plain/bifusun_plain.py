@@ -144,9 +144,36 @@ def route(z: torch.Tensor, r: dict) -> tuple[torch.Tensor, torch.Tensor]:
     return chosen, weight
 
 
-def routed_experts(h: torch.Tensor, w: dict, p: str, mlp: dict) -> torch.Tensor:
+def route_margin(z: torch.Tensor, r: dict) -> torch.Tensor:
+    """Per token, by how much the router's choice was decided: the smaller of the gap between the last group kept and the first one
+    dropped and the gap between the last expert chosen and the best one left out. A choice with a small margin may fall the other way
+    under another rounding, for no fault."""
+    E, top = r["experts"], r["top"]
+    s = torch.sigmoid(z)
+    margin = torch.full((z.shape[0],), float("inf"), dtype=z.dtype)
+    allowed = torch.ones_like(s, dtype=torch.bool)
+    groups = r.get("groups")
+    if groups and groups["count"] > 1:
+        per = E // groups["count"]
+        score = s.view(-1, groups["count"], per).topk(min(2, per), dim=-1).values.sum(-1)
+        ranked = score.sort(-1, descending=True)
+        if groups["keep"] < groups["count"]:
+            margin = ranked.values[:, groups["keep"] - 1] - ranked.values[:, groups["keep"]]
+        keep = torch.zeros_like(score, dtype=torch.bool).scatter_(1, ranked.indices[:, :groups["keep"]], True)
+        allowed = keep[:, :, None].expand(-1, -1, per).reshape(-1, E)
+    ranked = s.masked_fill(~allowed, -1.0).sort(-1, descending=True).values
+    if top < E:
+        gap = ranked[:, top - 1] - ranked[:, top].clamp_min(0.0)
+        margin = torch.minimum(margin, torch.where(ranked[:, top] >= 0, gap, torch.full_like(gap, float("inf"))))
+    return margin
+
+
+def routed_experts(h: torch.Tensor, w: dict, p: str, mlp: dict, margins: list | None = None) -> torch.Tensor:
     r = mlp["router"]
-    chosen, weight = route(h @ w[p + "router"].T, r)
+    z = h @ w[p + "router"].T
+    if margins is not None:
+        margins.append(route_margin(z, r))
+    chosen, weight = route(z, r)
     out = torch.zeros(h.shape[0], w[p + "e0.down"].shape[0], dtype=h.dtype)
     for t in range(h.shape[0]):
         for e, g in zip(chosen[t].tolist(), weight[t]):
@@ -156,8 +183,9 @@ def routed_experts(h: torch.Tensor, w: dict, p: str, mlp: dict) -> torch.Tensor:
 
 
 # ------------------------------------------------------------------------------------------------ the model
-def forward(cfg: dict, w: dict, ids: list[int], trace: list | None = None) -> torch.Tensor:
-    """Logits [T, vocab] of one sequence. ``trace`` (a list) receives the stream after every layer."""
+def forward(cfg: dict, w: dict, ids: list[int], trace: list | None = None, margins: list | None = None) -> torch.Tensor:
+    """Logits [T, vocab] of one sequence. ``trace`` (a list) receives the stream after every layer, ``margins`` every router's
+    :func:`route_margin` per token."""
     eps = cfg["norm"]["eps"]
     x = w["embed"][torch.tensor(ids)] * cfg.get("embedding", {}).get("scale", 1.0)
     shared: dict = {}
@@ -171,14 +199,19 @@ def forward(cfg: dict, w: dict, ids: list[int], trace: list | None = None) -> to
         else:
             raise ValueError(layer["type"])
         if layer.get("mlp") is not None:
-            x = x + routed_experts(rms_norm(x, w[p + "norm2"], eps), w, p + "mlp.", layer["mlp"])
+            x = x + routed_experts(rms_norm(x, w[p + "norm2"], eps), w, p + "mlp.", layer["mlp"], margins)
         if trace is not None:
             trace.append(x.clone())
     return (rms_norm(x, w["final.norm"], eps) @ w["head"].T) * cfg.get("logit_scale", 1.0)
 
 
-def greedy(cfg: dict, w: dict, prompt: list[int], n: int) -> list[int]:
-    ids = list(prompt)
+def greedy(cfg: dict, w: dict, prompt: list[int], n: int) -> tuple[list[int], list[float]]:
+    """``n`` greedy tokens after ``prompt``, and for each the gap between the two largest logits over the logits' spread (a near-tie
+    may fall either way under another rounding)."""
+    ids, gaps = list(prompt), []
     for _ in range(n):
-        ids.append(int(forward(cfg, w, ids)[-1].argmax()))
-    return ids[len(prompt):]
+        row = forward(cfg, w, ids)[-1]
+        best = row.topk(2).values
+        gaps.append(float((best[0] - best[1]) / row.std()))
+        ids.append(int(row.argmax()))
+    return ids[len(prompt):], gaps
