@@ -501,10 +501,11 @@ def bifusun_kernels(width: int, heads: int, kv_heads: int, head_dim: int, ff: in
         slots = i32([(r * (CTX // P)) * P + (i if len(q_lens) == 1 else CTX - 1) for r, x in enumerate(q_lens) for i in range(x)])
         ms = _time_ms(lambda: ops.qk_norm_rope_store(qkv, ones, ones, cos, cos, pos, slots, k_pool, v_pool, H, KV, D, 1e-6, status), flush=flush)
         put(f"qk_norm_rope_store {name}", None, ms, bytes_=n * C * 2 * 2)
+        state_slots = i32(list(range(len(q_lens))))
         ms = _time_ms(lambda: ops.conv_qkv_store(qkv, cq, ck, cv, conv=conv, bias=bias, tails=tails, k_pool=k_pool, v_pool=v_pool, slots=slots,
-                                                 req_of_token=req, cu_q=cu, state_slots=i32(list(range(len(q_lens)))), positions=pos,
-                                                 n_requests=len(q_lens), status=status, temp_coef=0.5, temp_every=128, blend=lam, first=first),
-                      flush=flush)
+                                                 req_of_token=req, cu_q=cu, state_slots=state_slots, positions=pos, n_requests=len(q_lens),
+                                                 status=status, temp_coef=0.5, temp_every=128, blend=lam, first=first,
+                                                 single_tokens=len(q_lens) > 1), flush=flush)
         put(f"conv_qkv_store {name} (bias, 4 taps, temperature, blend, cache write, tail roll)", f"qk_norm_rope_store {name}", ms,
             bytes_=n * (C * 2 * 2 + cv * 2) + len(q_lens) * C * (taps - 1) * 8)
 

@@ -63,6 +63,102 @@ __global__ void conv_qkv_store_kernel(
     if (store) v_pool[slot * cv + cc] = rounded;
 }
 
+
+// The same for bfloat16 with 16-byte accesses: a thread takes 8 neighbouring channels (all of q, of k or of v: the three widths are
+// multiples of 8). ROLL: every request brings exactly one token (a decode step), so the thread that filters a channel is the only one
+// that reads its tail and rolls it forward itself; otherwise the roll kernel follows.
+struct __align__(16) Bf16x8 { __nv_bfloat162 v[4]; };
+
+template <bool ROLL>
+__global__ void conv_qkv_store_bf16x8_kernel(
+    __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ v_out, const __nv_bfloat16* __restrict__ proj, int proj_stride, int cq, int ck,
+    int cv, int taps, const float* __restrict__ w, const float* __restrict__ bias, float* __restrict__ tails, long long slot_stride,
+    const int* __restrict__ req_of_token, const int* __restrict__ cu_q, const int* __restrict__ state_slots, const int* __restrict__ positions,
+    float temp_coef, int temp_every, const float* __restrict__ blend, const __nv_bfloat16* __restrict__ first, __nv_bfloat16* __restrict__ k_pool,
+    __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ slots, long long n_slots, int* status) {
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
+    const int t = blockIdx.x;
+    if (c >= cq + ck + cv) return;
+    const int r = ROLL ? t : req_of_token[t];
+    const int i = ROLL ? 0 : t - cu_q[r];
+    float b[8], acc[8], cur[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) b[k] = bias != nullptr ? bias[c + k] : 0.f;
+    auto load8 = [&](int row, float* out) {
+        const Bf16x8 raw = *reinterpret_cast<const Bf16x8*>(proj + (size_t)row * proj_stride + c);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __bfloat1622float2(raw.v[k]);
+            out[2 * k] = f.x + b[2 * k];
+            out[2 * k + 1] = f.y + b[2 * k + 1];
+        }
+    };
+    load8(t, cur);
+    float* tail = taps > 1 ? tails + (long long)state_slots[r] * slot_stride + (long long)c * (taps - 1) : nullptr;
+    if (taps <= 0) {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = cur[k];
+    } else {
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = w[(c + k) * taps + taps - 1] * cur[k];
+        for (int j = 0; j < taps - 1; ++j) {
+            const int back = taps - 1 - j;
+            float u[8];
+            if (i - back >= 0) {
+                load8(t - back, u);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) u[k] = tail[k * (taps - 1) + taps - 1 + (i - back)];
+            }
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] = fmaf(w[(c + k) * taps + j], u[k], acc[k]);
+        }
+        if (ROLL && taps > 1) {
+            for (int k = 0; k < 8; ++k) {
+                float* tk = tail + k * (taps - 1);
+                for (int e = 0; e + 1 < taps - 1; ++e) tk[e] = tk[e + 1];
+                tk[taps - 2] = cur[k];
+            }
+        }
+    }
+    auto pack = [&](const float* x) {
+        Bf16x8 out;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) out.v[k] = __floats2bfloat162_rn(x[2 * k], x[2 * k + 1]);
+        return out;
+    };
+    if (c < cq) {
+        if (temp_every > 0) {
+            const float f = 1.f + temp_coef * logf((float)((positions[t] + 1) / temp_every + 1));
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] *= f;
+        }
+        *reinterpret_cast<Bf16x8*>(q_out + (size_t)t * cq + c) = pack(acc);
+        return;
+    }
+    const long long slot = slots[t];
+    if (slot >= n_slots) oxr_report(status, OXR_BAD_SLOT, t);
+    const bool store = slot >= 0 && slot < n_slots;
+    if (c < cq + ck) {
+        if (store) *reinterpret_cast<Bf16x8*>(k_pool + slot * ck + (c - cq)) = pack(acc);
+        return;
+    }
+    const int cc = c - cq - ck;
+    if (blend != nullptr) {
+        const float lam = blend[0];
+        const Bf16x8 raw = *reinterpret_cast<const Bf16x8*>(first + (size_t)t * cv + cc);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __bfloat1622float2(raw.v[k]);
+            acc[2 * k] = (1.f - lam) * acc[2 * k] + lam * f.x;
+            acc[2 * k + 1] = (1.f - lam) * acc[2 * k + 1] + lam * f.y;
+        }
+    }
+    const Bf16x8 rounded = pack(acc);
+    if (v_out != nullptr) *reinterpret_cast<Bf16x8*>(v_out + (size_t)t * cv + cc) = rounded;
+    if (store) *reinterpret_cast<Bf16x8*>(v_pool + slot * cv + cc) = rounded;
+}
+
 // After the convolution read it: the tail becomes the last taps-1 values of (old tail ++ the step's proj + bias).
 template <typename T>
 __global__ void conv_qkv_roll_kernel(float* __restrict__ tails, long long slot_stride, const T* __restrict__ proj, int proj_stride, int channels,
@@ -84,7 +180,7 @@ OXR_API int oxr_conv_qkv_store(void* q_out, void* v_out, const void* proj, int n
                                int taps, const float* w, const float* bias, float* tails, long long slot_stride, const int* req_of_token,
                                const int* cu_q, const int* state_slots, const int* positions, float temp_coef, int temp_every,
                                const float* blend, const void* first, void* k_pool, void* v_pool, const int* slots, long long n_slots, int dtype,
-                               int* status, cudaStream_t stream) {
+                               int single_tokens, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const int channels = cq + ck + cv;
     if (cq <= 0 || ck <= 0 || cv <= 0 || taps < 0 || proj_stride < channels || n_requests <= 0 || (taps > 0 && w == nullptr) ||
@@ -102,6 +198,26 @@ OXR_API int oxr_conv_qkv_store(void* q_out, void* v_out, const void* proj, int n
             conv_qkv_roll_kernel<T><<<roll, threads, 0, stream>>>(tails, slot_stride, (const T*)proj, proj_stride, channels, taps, bias, cu_q, \
                                                                  state_slots); \
     } while (0)
+    const auto aligned = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
+    if (dtype == 1 && cq % 8 == 0 && ck % 8 == 0 && cv % 8 == 0 && proj_stride % 8 == 0 && aligned(proj) && aligned(q_out) && aligned(v_out) &&
+        aligned(first) && aligned(k_pool) && aligned(v_pool)) {
+        using B = __nv_bfloat16;
+        dim3 vgrid(n_tokens, (channels / 8 + threads - 1) / threads);
+        const bool single = n_tokens == n_requests && single_tokens;
+#define OXR_CONV_QKV8(ROLL) \
+        conv_qkv_store_bf16x8_kernel<ROLL><<<vgrid, threads, 0, stream>>>((B*)q_out, (B*)v_out, (const B*)proj, proj_stride, cq, ck, cv, taps, w, bias, \
+                                                                         tails, slot_stride, req_of_token, cu_q, state_slots, positions, temp_coef, \
+                                                                         temp_every, blend, (const B*)first, (B*)k_pool, (B*)v_pool, slots, n_slots, status)
+        if (single) {
+            OXR_CONV_QKV8(true);
+        } else {
+            OXR_CONV_QKV8(false);
+            if (taps > 1)
+                conv_qkv_roll_kernel<B><<<roll, threads, 0, stream>>>(tails, slot_stride, (const B*)proj, proj_stride, channels, taps, bias, cu_q, state_slots);
+        }
+#undef OXR_CONV_QKV8
+        return oxr_launch_status();
+    }
     if (dtype == 0) OXR_CONV_QKV(float);
     else OXR_CONV_QKV(__nv_bfloat16);
 #undef OXR_CONV_QKV

@@ -5,6 +5,9 @@
 // of the `keep` best groups can be chosen. The `top` allowed experts with the largest s are chosen (the lower index wins a
 // tie); their weights are their s divided by the sum of the chosen s (+ 1e-20), times `scale`. All of it in fp32.
 //
+// For steps of many tokens the experts run one after the other instead, each over the tokens that chose it (`expert_sort`, `gather_rows`,
+// then per expert two products and the activation, then `combine_rows`): the work is then that of the chosen experts only.
+//
 // The choice leaves the kernel twice: as lists (expert ids and weights, [tokens, top]) and as a dense row per token
 // (gate [tokens, E]: the weight of a chosen expert, 0 for the others). With the dense row the experts run as two
 // products over ALL experts' stacked weights: u = h W_up^T [tokens, E ff], a = gate[expert of the column] act(u), and
@@ -84,7 +87,7 @@ __global__ void gated_relu2_kernel(T* __restrict__ a, const T* __restrict__ u, c
     if (i >= total) return;
     const size_t t = i / cols;
     const int c = (int)(i - t * cols);
-    const float g = gate[t * E + c / ff];
+    const float g = gate != nullptr ? gate[t * E + c / ff] : 1.f;
     const float v = fmaxf(Num<T>::to_f32(u[i]), 0.f);
     a[i] = Num<T>::from_f32(g * (v * v));
 }
@@ -96,5 +99,95 @@ OXR_API int oxr_gated_relu2(void* a, const void* u, const float* gate, int n_tok
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == 0) gated_relu2_kernel<float><<<blocks, 256, 0, stream>>>((float*)a, (const float*)u, gate, total, E * ff, ff, E);
     else gated_relu2_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)a, (const __nv_bfloat16*)u, gate, total, E * ff, ff, E);
+    return oxr_launch_status();
+}
+
+// ---------------------------------------------------------------------------------------------- tokens grouped by expert
+// One block orders the (token, choice) pairs by expert: a histogram in shared memory, its running sum, then every pair takes the
+// next free place of its expert (pairs of one expert end up in no particular order: each row's result does not depend on where
+// in its expert's stretch it stands).
+constexpr int SORT_MAX_EXPERTS = 1024;
+
+__global__ void __launch_bounds__(1024) expert_sort_kernel(int* __restrict__ counts, int* __restrict__ order, int* __restrict__ place,
+                                                          const int* __restrict__ ids, int total, int E) {
+    __shared__ int hist[SORT_MAX_EXPERTS], cursor[SORT_MAX_EXPERTS];
+    for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
+    __syncthreads();
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {
+        const int e = ids[i];
+        if (e >= 0 && e < E) atomicAdd(&hist[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int at = 0;
+        for (int e = 0; e < E; ++e) {
+            cursor[e] = at;
+            counts[e] = hist[e];
+            at += hist[e];
+        }
+    }
+    __syncthreads();
+    for (int i = threadIdx.x; i < total; i += blockDim.x) {
+        const int e = ids[i];
+        if (e >= 0 && e < E) {
+            const int at = atomicAdd(&cursor[e], 1);
+            order[at] = i;
+            place[i] = at;
+        } else {
+            place[i] = -1;
+        }
+    }
+}
+
+OXR_API int oxr_expert_sort(int* counts, int* order, int* place, const int* ids, int total, int E, cudaStream_t stream) {
+    if (total <= 0) return 0;
+    if (E <= 0 || E > SORT_MAX_EXPERTS) return OXR_BAD_ARGUMENT;
+    expert_sort_kernel<<<1, 1024, 0, stream>>>(counts, order, place, ids, total, E);
+    return oxr_launch_status();
+}
+
+// out[i] = x[order[i] / per_row]: 16-byte copies where the rows allow them
+template <typename T>
+__global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ x, const int* __restrict__ order, int width, int per_row) {
+    const size_t dst = (size_t)blockIdx.x * width, src = (size_t)(order[blockIdx.x] / per_row) * width;
+    const bool wide = (width * sizeof(T)) % 16 == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)x & 15) == 0;
+    if (wide) {
+        const int4* s4 = reinterpret_cast<const int4*>(x + src);
+        int4* d4 = reinterpret_cast<int4*>(out + dst);
+        for (int i = threadIdx.x; i < (int)(width * sizeof(T) / 16); i += blockDim.x) d4[i] = s4[i];
+    } else {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) out[dst + i] = x[src + i];
+    }
+}
+
+OXR_API int oxr_gather_rows(void* out, const void* x, const int* order, int rows, int width, int per_row, int dtype, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (width <= 0 || per_row <= 0) return OXR_BAD_ARGUMENT;
+    if (dtype == 0) gather_rows_kernel<float><<<rows, 128, 0, stream>>>((float*)out, (const float*)x, order, width, per_row);
+    else gather_rows_kernel<__nv_bfloat16><<<rows, 128, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)x, order, width, per_row);
+    return oxr_launch_status();
+}
+
+// out[t] = sum_j weights[t, j] * y[place[t top + j]], summed in fp32 in the order of j, rounded once
+template <typename T>
+__global__ void combine_rows_kernel(T* __restrict__ out, const T* __restrict__ y, const int* __restrict__ place, const float* __restrict__ weights,
+                                    int top, int width) {
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float acc = 0.f;
+        for (int j = 0; j < top; ++j) {
+            const int at = place[(size_t)t * top + j];
+            if (at >= 0) acc = fmaf(weights[(size_t)t * top + j], Num<T>::to_f32(y[(size_t)at * width + c]), acc);
+        }
+        out[(size_t)t * width + c] = Num<T>::from_f32(acc);
+    }
+}
+
+OXR_API int oxr_combine_rows(void* out, const void* y, const int* place, const float* weights, int n_tokens, int top, int width, int dtype,
+                             cudaStream_t stream) {
+    if (n_tokens <= 0) return 0;
+    if (top <= 0 || width <= 0) return OXR_BAD_ARGUMENT;
+    if (dtype == 0) combine_rows_kernel<float><<<n_tokens, 256, 0, stream>>>((float*)out, (const float*)y, place, weights, top, width);
+    else combine_rows_kernel<__nv_bfloat16><<<n_tokens, 256, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)y, place, weights, top, width);
     return oxr_launch_status();
 }

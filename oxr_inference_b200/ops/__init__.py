@@ -138,17 +138,20 @@ def _lib():
         lib.oxr_scatter_rows.argtypes = [p, ll, ll, p, i, i, i, p, i, i, p, p, ll, i, p]
         lib.oxr_latent_prep.argtypes = [p, ll, ll, p, i, i, p, f, p, i, i, i, p, i, i, p, p, i, p, i, i, p, p]
         lib.oxr_head_linear.argtypes = [p, i, i, p, i, i, p, i, i, i, i, i, p]
-        lib.oxr_conv_qkv_store.argtypes = [p, p, p, i, i, i, i, i, i, i, p, p, p, ll, p, p, p, p, f, i, p, p, p, p, p, ll, i, p, p]
+        lib.oxr_conv_qkv_store.argtypes = [p, p, p, i, i, i, i, i, i, i, p, p, p, ll, p, p, p, p, f, i, p, p, p, p, p, ll, i, i, p, p]
         lib.oxr_add_bias.argtypes = [p, p, i, i, i, p]
         lib.oxr_scale_f32.argtypes = [p, f, ll, p]
-        lib.oxr_mlstm_scan.argtypes = [p, p, i, i, i, i, i, p, p, i, i, i, f, f, p, ll, p, p, i, p]
+        lib.oxr_mlstm_scan.argtypes = [p, p, p, i, i, i, i, i, p, p, i, i, i, f, f, p, ll, p, p, i, p]
         lib.oxr_head_norm_gate.argtypes = [p, p, p, i, i, i, p, i, i, f, i, p]
         lib.oxr_route.argtypes = [p, p, p, p, i, i, i, i, i, f, p]
         lib.oxr_gated_relu2.argtypes = [p, p, p, i, i, i, i, p]
+        lib.oxr_expert_sort.argtypes = [p, p, p, p, i, i, p]
+        lib.oxr_gather_rows.argtypes = [p, p, p, i, i, i, i, p]
+        lib.oxr_combine_rows.argtypes = [p, p, p, p, i, i, i, i, p]
         for name in ("oxr_stream_rms_norm", "oxr_norm_add_norm", "oxr_concat2_cast", "oxr_add_row_f32", "oxr_clamped_glu", "oxr_rotary_angles",
                      "oxr_mamba_conv", "oxr_mamba_scan", "oxr_gated_group_norm", "oxr_attention_rows", "oxr_scatter_rows", "oxr_latent_prep",
                      "oxr_head_linear", "oxr_conv_qkv_store", "oxr_add_bias", "oxr_scale_f32", "oxr_mlstm_scan", "oxr_head_norm_gate", "oxr_route",
-                     "oxr_gated_relu2"):
+                     "oxr_gated_relu2", "oxr_expert_sort", "oxr_gather_rows", "oxr_combine_rows"):
             getattr(lib, name).restype = c_int
         for name in ("oxr_embedding", "oxr_add_rms_norm", "oxr_silu_mul", "oxr_cast", "oxr_qk_norm_rope_store",
                      "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_gemm_skinny_gated_bf16", "oxr_gemm_stream_bf16", "oxr_gemm_stream_gated_bf16", "oxr_gemm_tcgen05_bf16", "oxr_gemm_tcgen05_pair_bf16", "oxr_gemm_tcgen05_gated_bf16", "oxr_gemm_few_rows_cluster_bf16", "oxr_gemm_few_rows_max_clusters",
@@ -834,13 +837,13 @@ def _gemm_split_buffers(device: torch.device) -> tuple[torch.Tensor, torch.Tenso
     return got
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
+def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None, out: torch.Tensor | None = None) -> torch.Tensor:
     """``x @ weight.T`` for ``weight [out, in]``, no bias (oxr_runtime/language.py:223-231), fp32 accumulation.
 
     float32 x float32 runs the fp32 CUDA-core kernel (no TF32). bfloat16 x bfloat16 runs the skinny kernel up to
     ``SKINNY_MAX_ROWS`` rows and the TMA + tcgen05 kernel beyond (cuBLAS only when a row is not a whole number of
     16-byte words). A weight kept in float32 under bfloat16 activations is multiplied in fp32 and the result
-    rounded once.
+    rounded once. ``out`` (contiguous ``[rows, out]`` of the output dtype) receives the product instead of a new tensor.
     """
     if isinstance(x, NormedLazily):
         out = _scaled_linear(x, weight, gated=False) if out_dtype in (None, torch.bfloat16) else None
@@ -854,26 +857,34 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
     if k != k2:
         raise KernelError(f"linear: x has {k} columns, weight has {k2}")
     out_dtype = out_dtype or x.dtype
+    if out is not None:
+        _need(out, "out", out_dtype)
+        if out.shape != (m, n):
+            raise KernelError(f"linear: out is {tuple(out.shape)} for a product of {(m, n)}")
+    given = out
     lib = _lib()
     if weight.dtype == torch.float32:
         x32 = cast(x, torch.float32)
-        out = torch.empty((m, n), dtype=torch.float32, device=x.device)
+        out = given if given is not None and out_dtype == torch.float32 else torch.empty((m, n), dtype=torch.float32, device=x.device)
         _done(lib.oxr_gemm_f32_nt(out.data_ptr(), x32.data_ptr(), weight.data_ptr(), m, n, k, _stream()), "gemm_f32")
+        if given is not None and out_dtype != torch.float32:
+            given.copy_(out)
+            return given
         return cast(out, out_dtype)
     if x.dtype != torch.bfloat16:
         raise KernelError(f"linear: activations {x.dtype} with weight {weight.dtype} is not a supported pair")
     if STREAM_GEMM and m <= STREAM_MAX_ROWS and k % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
-        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+        out = given if given is not None else torch.empty((m, n), dtype=out_dtype, device=x.device)
         _done(lib.oxr_gemm_stream_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _DT[out_dtype],
                                        new_status(x.device).data_ptr(), _stream()), "gemm_stream")
         return out
     if m <= SKINNY_MAX_ROWS and k % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
-        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+        out = given if given is not None else torch.empty((m, n), dtype=out_dtype, device=x.device)
         _done(lib.oxr_gemm_skinny_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _DT[out_dtype], _stream()),
               "gemm_skinny")
         return out
     if k % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0:
-        out = torch.empty((m, n), dtype=out_dtype, device=x.device)
+        out = given if given is not None else torch.empty((m, n), dtype=out_dtype, device=x.device)
         few = _gemm_few_rows_plan(m, n, k)
         if few:
             _done(lib.oxr_gemm_few_rows_cluster_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, _DT[out_dtype], few,
@@ -895,9 +906,11 @@ def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None 
         _done(code, "gemm_tcgen05")
         return out
     # rows that are not whole 16-byte words cannot be fetched by TMA: the library product takes them
-    if out_dtype == torch.float32:
-        return torch.mm(x, weight.t(), out_dtype=torch.float32)
-    return torch.mm(x, weight.t())
+    got = torch.mm(x, weight.t(), out_dtype=torch.float32) if out_dtype == torch.float32 else torch.mm(x, weight.t())
+    if given is not None:
+        given.copy_(got)
+        return given
+    return got
 
 
 FUSE_MAX_ROWS = min(16, int(os.environ.get("OXR_B200_FUSE_ROWS", "16")))
@@ -1242,15 +1255,16 @@ def attention_rows(q: torch.Tensor, num_heads: int, k_pool: torch.Tensor, v_pool
 def conv_qkv_store(proj: torch.Tensor, cq: int, ck: int, cv: int, *, conv: torch.Tensor | None, bias: torch.Tensor | None, tails: torch.Tensor | None,
                    k_pool: torch.Tensor, v_pool: torch.Tensor, slots: torch.Tensor, req_of_token: torch.Tensor, cu_q: torch.Tensor,
                    state_slots: torch.Tensor, positions: torch.Tensor, n_requests: int, status: torch.Tensor, temp_coef: float = 0.0,
-                   temp_every: int = 0, blend: torch.Tensor | None = None, first: torch.Tensor | None = None, keep_values: bool = False
-                   ) -> tuple[torch.Tensor, torch.Tensor | None]:
+                   temp_every: int = 0, blend: torch.Tensor | None = None, first: torch.Tensor | None = None, keep_values: bool = False,
+                   single_tokens: bool = False) -> tuple[torch.Tensor, torch.Tensor | None]:
     """From a packed step's stacked projection ``proj [tokens, >= cq + ck + cv]`` to queries and cache rows in one launch (and one more that
     rolls the tails): add ``bias [cq + ck + cv]``, filter every channel causally with ``conv [channels, taps]`` (the last tap meets the current
     token; what stands before a step's first token comes from the request's ``tails`` row ``[channels, taps - 1]``, zero for a new request,
     which is rolled forward), multiply the queries by ``1 + temp_coef ln(floor((p + 1) / temp_every) + 1)`` (``temp_every`` 0: not), blend the
     values as ``(1 - blend) v + blend first`` (``blend``: one fp32 number on the device; ``first [tokens, cv]``), and write keys and values to
-    ``k_pool`` / ``v_pool`` (one layer's ``[pages, page_size, KV, D]``) at ``slots`` (-1 skips). ``conv`` None: no filter. Returns the queries
-    ``[tokens, cq]`` and, with ``keep_values``, the values ``[tokens, cv]`` as they were cached."""
+    ``k_pool`` / ``v_pool`` (one layer's ``[pages, page_size, KV, D]``) at ``slots`` (-1 skips). ``conv`` None: no filter. ``single_tokens``: the
+    caller knows that every request brings exactly one token (token r is request r's); the bfloat16 kernel then rolls the tails itself.
+    Returns the queries ``[tokens, cq]`` and, with ``keep_values``, the values ``[tokens, cv]`` as they were cached."""
     _need(proj, "proj")
     _need(k_pool, "k_pool", proj.dtype)
     _need(v_pool, "v_pool", proj.dtype)
@@ -1281,9 +1295,9 @@ def conv_qkv_store(proj: torch.Tensor, cq: int, ck: int, cv: int, *, conv: torch
                                     _ptr(tails), tails.stride(0) if tails is not None else 0, req_of_token.data_ptr(), cu_q.data_ptr(),
                                     state_slots.data_ptr(), positions.data_ptr(), float(temp_coef), int(temp_every), _ptr(blend), _ptr(first),
                                     k_pool.data_ptr(), v_pool.data_ptr(), slots.data_ptr(), k_pool.shape[0] * k_pool.shape[1], _dtype_code(proj),
-                                    status.data_ptr(), _stream()), "conv_qkv_store")
+                                    int(bool(single_tokens) and n == n_requests), status.data_ptr(), _stream()), "conv_qkv_store")
     global launch_count
-    launch_count += 1 if taps > 1 else 0
+    launch_count += 1 if taps > 1 and not (single_tokens and n == n_requests and proj.dtype == torch.bfloat16) else 0
     return q, v
 
 
@@ -1321,7 +1335,10 @@ def mlstm_scan(proj: torch.Tensor, q_col0: int, k_col0: int, v_col0: int, gates:
     if gates.shape != (n, 2 * heads) or gate_bias.numel() != 2 * heads:
         raise KernelError("mlstm_scan: gates must be [tokens, 2 * heads] with one bias each")
     y = torch.empty((n, heads * value_dim), dtype=torch.float32, device=proj.device)
-    _done(_lib().oxr_mlstm_scan(y.data_ptr(), proj.data_ptr(), n_requests, proj.shape[1], q_col0, k_col0, v_col0, gates.data_ptr(), gate_bias.data_ptr(),
+    coef = torch.empty((n, heads, 3), dtype=torch.float32, device=proj.device)   # per token and head: what the gate kernel hands the recurrence
+    global launch_count
+    launch_count += 1
+    _done(_lib().oxr_mlstm_scan(y.data_ptr(), coef.data_ptr(), proj.data_ptr(), n_requests, proj.shape[1], q_col0, k_col0, v_col0, gates.data_ptr(), gate_bias.data_ptr(),
                                 heads, key_dim, value_dim, float(cap), float(q_scale), state.data_ptr(), state.stride(0), cu_q.data_ptr(),
                                 state_slots.data_ptr(), _dtype_code(proj), _stream()), "mlstm_scan")
     return y
@@ -1358,14 +1375,54 @@ def route(z: torch.Tensor, *, top: int, groups: int, keep: int, scale: float) ->
     return gate, ids, wts
 
 
-def gated_relu2(u: torch.Tensor, gate: torch.Tensor, ff: int) -> torch.Tensor:
-    """``a[t, c] = gate[t, c // ff] * relu(u[t, c])^2`` for the stacked up-projections ``u [tokens, E * ff]`` of all experts."""
+def gated_relu2(u: torch.Tensor, gate: torch.Tensor | None, ff: int, out: torch.Tensor | None = None) -> torch.Tensor:
+    """``a[t, c] = gate[t, c // ff] * relu(u[t, c])^2`` for the stacked up-projections ``u [tokens, E * ff]`` of all experts; ``gate`` None: plain
+    ``relu(u)^2``. ``out`` may be ``u`` itself."""
     _need(u, "u")
-    _need(gate, "gate", torch.float32)
     n, cols = u.shape
-    E = gate.shape[1]
-    if cols != E * ff or gate.shape[0] != n:
+    E = cols // ff
+    if gate is not None:
+        _need(gate, "gate", torch.float32)
+        if gate.shape != (n, E):
+            raise KernelError("gated_relu2: sizes do not fit")
+    if cols != E * ff:
         raise KernelError("gated_relu2: sizes do not fit")
-    a = torch.empty_like(u)
-    _done(_lib().oxr_gated_relu2(a.data_ptr(), u.data_ptr(), gate.data_ptr(), n, E, int(ff), _dtype_code(u), _stream()), "gated_relu2")
+    a = torch.empty_like(u) if out is None else out
+    _done(_lib().oxr_gated_relu2(a.data_ptr(), u.data_ptr(), _ptr(gate), n, E, int(ff), _dtype_code(u), _stream()), "gated_relu2")
     return a
+
+
+def expert_sort(ids: torch.Tensor, experts: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """The (token, choice) pairs of ``ids [tokens, top]`` ordered by expert: ``counts [experts]`` (int32), ``order [tokens * top]`` (the flat pair
+    index at each place of the ordered list) and ``place [tokens * top]`` (its inverse). Pairs of one expert stand in no particular order."""
+    _need(ids, "ids", torch.int32)
+    total = ids.numel()
+    counts = torch.empty(experts, dtype=torch.int32, device=ids.device)
+    order = torch.empty(total, dtype=torch.int32, device=ids.device)
+    place = torch.empty(total, dtype=torch.int32, device=ids.device)
+    _done(_lib().oxr_expert_sort(counts.data_ptr(), order.data_ptr(), place.data_ptr(), ids.data_ptr(), total, int(experts), _stream()), "expert_sort")
+    return counts, order, place
+
+
+def gather_rows(x: torch.Tensor, order: torch.Tensor, per_row: int) -> torch.Tensor:
+    """``out[i] = x[order[i] // per_row]``: the rows of ``x`` repeated and put in the order of a sorted list of (row, choice) pairs."""
+    _need(x, "x")
+    _need(order, "order", torch.int32)
+    out = torch.empty((order.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    _done(_lib().oxr_gather_rows(out.data_ptr(), x.data_ptr(), order.data_ptr(), order.numel(), x.shape[1], int(per_row), _dtype_code(x), _stream()),
+          "gather_rows")
+    return out
+
+
+def combine_rows(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+    """``out[t] = sum_j weights[t, j] * y[place[t * top + j]]`` with the sum in fp32 in the order of j; ``y [tokens * top, width]``."""
+    _need(y, "y")
+    _need(place, "place", torch.int32)
+    _need(weights, "weights", torch.float32)
+    n, top = weights.shape
+    if place.numel() != n * top or y.shape[0] != n * top:
+        raise KernelError("combine_rows: sizes do not fit")
+    out = torch.empty((n, y.shape[1]), dtype=y.dtype, device=y.device)
+    _done(_lib().oxr_combine_rows(out.data_ptr(), y.data_ptr(), place.data_ptr(), weights.data_ptr(), n, top, y.shape[1], _dtype_code(y), _stream()),
+          "combine_rows")
+    return out

@@ -15,13 +15,20 @@ class RoutedExperts(FeedForward):
     largest scores, and only experts of the ``keep`` best groups can be chosen. Each token runs the ``top`` allowed experts with the
     largest scores; their outputs are added with weights ``s / (sum of the chosen s + 1e-20) * scale``.
 
-    All experts' up-projections are stacked into one matrix ``[experts * ff, hidden]`` and their down-projections side by side into
-    ``[hidden, experts * ff]``, so the layer is two products for any batch: the activation kernel multiplies each expert's stretch of
-    columns by the token's weight for that expert (zero when it was not chosen), and the sum over experts happens inside the second
-    product's reduction. A token's result does not depend on what else is in the batch."""
+    Two forms. Few tokens (decode steps, short portions; also whatever is captured in a CUDA graph): all experts' up-projections are
+    stacked into one matrix ``[experts * ff, hidden]`` and their down-projections side by side into ``[hidden, experts * ff]``, so the layer
+    is two products whatever the choices: the activation kernel multiplies each expert's stretch of columns by the token's weight for that
+    expert (zero when it was not chosen), and the sum over experts happens inside the second product's reduction. With a handful of tokens
+    nearly every expert is chosen by someone, and the products are bound by reading the weights, which this form reads exactly once.
+    From ``grouped_min_rows`` tokens on the work of the experts nobody chose would dominate, so the (token, choice) pairs are ordered by
+    expert on the device, the host reads how many each expert got (one synchronisation per layer), and every expert multiplies just its own
+    rows; a last kernel adds each token's ``top`` results with their weights in the order of the choices. Either way a token's result does
+    not depend on what else is in the batch beyond rounding."""
+
+    GROUPED_MIN_ROWS = 256
 
     def __init__(self, runtime: Runtime, *, hidden_size: int, intermediate_size: int, experts: int, top: int, groups: int = 1, keep: int = 1,
-                 scale: float = 1.0):
+                 scale: float = 1.0, grouped_min_rows: int | None = None):
         self.runtime = runtime
         self.hidden, self.ff, self.E, self.top = int(hidden_size), int(intermediate_size), int(experts), int(top)
         self.groups, self.keep, self.scale = int(groups), int(keep), float(scale)
@@ -31,8 +38,10 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"{self.keep} of {self.groups} groups cannot be kept")
         if not 1 <= self.top <= self.keep * (self.E // self.groups):
             raise ValueError(f"{self.top} experts cannot be chosen from {self.keep} groups of {self.E // self.groups}")
+        self.grouped_min_rows = self.GROUPED_MIN_ROWS if grouped_min_rows is None else int(grouped_min_rows)
         self.up: torch.Tensor | None = None       # [E * ff, hidden]
         self.down: torch.Tensor | None = None     # [hidden, E * ff]
+        self.down_by_expert: torch.Tensor | None = None   # [E, hidden, ff]: made at the first grouped step
         self.router: torch.Tensor | None = None   # [E, hidden]
 
     def parameters(self) -> dict[str, ParamInfo]:
@@ -67,6 +76,24 @@ class RoutedExperts(FeedForward):
 
     def forward(self, h: torch.Tensor) -> torch.Tensor:
         z = ops.linear(h, self.router, torch.float32)
-        gate, _, _ = ops.route(z, top=self.top, groups=self.groups, keep=self.keep, scale=self.scale)
+        gate, ids, weights = ops.route(z, top=self.top, groups=self.groups, keep=self.keep, scale=self.scale)
+        if self.top < self.E and h.shape[0] >= self.grouped_min_rows > 0 and not torch.cuda.is_current_stream_capturing():
+            return self._grouped(h, ids, weights)
         u = ops.linear(h, self.up)
         return ops.linear(ops.gated_relu2(u, gate, self.ff), self.down)
+
+    def _grouped(self, h: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
+        """Every expert over the rows that chose it."""
+        if self.down_by_expert is None:
+            # a second copy of the down-projections, expert by expert (the stacked one is laid out for the single product)
+            self.down_by_expert = self.down.view(self.hidden, self.E, self.ff).permute(1, 0, 2).contiguous()
+        counts, order, place = ops.expert_sort(ids, self.E)
+        x = ops.gather_rows(h, order, self.top)                  # [tokens * top, hidden], ordered by expert
+        y = torch.empty((x.shape[0], self.hidden), dtype=x.dtype, device=x.device)
+        at = 0
+        for e, c in enumerate(counts.tolist()):                  # the step's one synchronisation of this layer
+            if c:
+                u = ops.linear(x[at:at + c], self.up[e * self.ff:(e + 1) * self.ff])
+                ops.linear(ops.gated_relu2(u, None, self.ff, out=u), self.down_by_expert[e], out=y[at:at + c])
+                at += c
+        return ops.combine_rows(y, place, weights)

@@ -171,7 +171,7 @@ class MaskedAttention(Mixer):
                 qkv, self.cq, self.ck, self.cv, conv=self.qkv_conv, bias=self.qkv_bias, tails=cache.state, k_pool=k_pool, v_pool=v_pool,
                 slots=group.slots if cache.store else ctx.no_store_slots, req_of_token=ctx.req_of_token, cu_q=ctx.cu_q,
                 state_slots=ctx.state_slots, positions=ctx.positions, n_requests=ctx.n_requests, status=ctx.status, temp_coef=self.temp_coef,
-                temp_every=self.temp_every, blend=blend, first=first, keep_values=self.value_mix == "keep")
+                temp_every=self.temp_every, blend=blend, first=first, keep_values=self.value_mix == "keep", single_tokens=ctx.single_tokens)
             if self.value_mix == "keep":
                 ctx.shared[self.value_mix_key] = kept
             q_width = self.cq

@@ -569,3 +569,83 @@ def test_marked_keys_with_values_of_another_size(dtype):
     ops.check_status(status)
     shifted = _plain_attention(q, keys, values, [max(0, p - 1) for p in queries], 0.5)
     assert (shifted - want).abs().max() > 0.1
+
+
+# ------------------------------------------------------------------------------------------------ experts over the rows that chose them
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("E,top,groups,keep,n", [(6, 2, 3, 2, 37), (12, 4, 4, 3, 300), (5, 1, 1, 1, 64), (8, 3, 2, 1, 9)])
+def test_experts_grouped_by_expert_equal_the_single_product_and_the_plain_sum(dtype, E, top, groups, keep, n):
+    """The form for many tokens (pairs ordered by expert, each expert over its own rows, weighted sum) against the form for few (one
+    product over all experts) and against the plain sum; some experts get no row at all."""
+    from oxr_inference_b200 import ops
+    from oxr_inference_b200.parts.base import Runtime
+    from oxr_inference_b200.parts.experts import RoutedExperts
+
+    g = torch.Generator().manual_seed(E * 10 + top)
+    width, ff = 48, 16
+    rt = Runtime(device=torch.device(DEV), dtype=dtype, max_positions=1, status=ops.new_status(DEV))
+    part = RoutedExperts(rt, hidden_size=width, intermediate_size=ff, experts=E, top=top, groups=groups, keep=keep, scale=1.5, grouped_min_rows=1)
+    w = {name: (torch.randn(info.shape, generator=g) * (0.8 if name == "router" else 0.2)).to(torch.bfloat16) for name, info in part.parameters().items()}
+    w["router"][E - 1] -= 3.0          # the last expert is hardly ever chosen
+    for name, t in w.items():
+        part.assign(name, t)
+    h = torch.randn(n, width, generator=g).to(dtype)
+    grouped = part.forward(h.to(DEV)).float().cpu()
+    part.grouped_min_rows = 0
+    single = part.forward(h.to(DEV)).float().cpu()
+    r = {"experts": E, "top": top, "scale": 1.5}
+    if groups > 1:
+        r["groups"] = {"count": groups, "keep": keep}
+    plain_w = {"mlp." + k: v.double() for k, v in w.items()}
+    want = BP.routed_experts(h.double(), plain_w, "mlp.", {"router": r})
+    margin = BP.route_margin(h.double() @ plain_w["mlp.router"].T, r)
+    clear = margin > (1e-4 if dtype == torch.float32 else 2e-2)
+    assert clear.float().mean() > 0.5
+    tol = (1e-4 if dtype == torch.float32 else 3e-2) * float(want.abs().max())
+    assert (grouped - want)[clear].abs().max() <= tol
+    assert (single - want)[clear].abs().max() <= tol
+
+
+def test_expert_sort_gather_and_combine():
+    from oxr_inference_b200 import ops
+
+    g = torch.Generator().manual_seed(4)
+    n, top, E, width = 150, 3, 7, 24
+    ids = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(n)]).to(torch.int32)
+    counts, order, place = ops.expert_sort(ids.to(DEV), E)
+    counts, order, place = counts.cpu(), order.cpu().long(), place.cpu().long()
+    assert torch.equal(counts.long(), torch.bincount(ids.view(-1).long(), minlength=E))
+    assert torch.equal(order[place], torch.arange(n * top))
+    sorted_experts = ids.view(-1)[order]
+    assert torch.all(sorted_experts[1:] >= sorted_experts[:-1])
+    x = torch.randn(n, width, generator=g).to(torch.bfloat16)
+    rows = ops.gather_rows(x.to(DEV), order.to(torch.int32).to(DEV), top).cpu()
+    assert torch.equal(rows, x[order // top])
+    y = torch.randn(n * top, width, generator=g)
+    wts = torch.rand(n, top, generator=g)
+    got = ops.combine_rows(y.to(DEV), place.to(torch.int32).to(DEV), wts.to(DEV)).cpu()
+    want = (y[place].view(n, top, width).double() * wts.double()[:, :, None]).sum(1)
+    assert (got - want).abs().max() < 1e-5
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_whole_model_with_experts_grouped_from_few_rows_on(dtype, tmp_path, monkeypatch):
+    """A whole model whose feed-forwards take the grouped form from 8 tokens on: whole prompt, portions on both sides of that limit, and
+    two requests in one step."""
+    from oxr_inference_b200.parts.experts import RoutedExperts
+
+    monkeypatch.setattr(RoutedExperts, "GROUPED_MIN_ROWS", 8)
+    cfg = BU.MODEL_P
+    folder = BU.make_folder(tmp_path, cfg, "P", seed=13)
+    ids = BU.tokens(cfg, 90, seed=6)
+    want, mg = BU.plain_logits(folder, ids), BU.router_margins(folder, ids)
+    r = runner_for(folder, dtype)
+    close(run_cut(r, ids, [90]), want, dtype, "whole prompt", mg)
+    close(run_cut(r, ids, [7, 8, 9, 30, 1, 1, 34]), want, dtype, "portions", mg)
+    other = BU.tokens(cfg, 20, seed=7)
+    a, b = r.cache.open("a"), r.cache.open("b")
+    got = r.step([feed(r, a, ids, 0, 50), feed(r, b, other, 0, 20)])
+    close(got[:50], want[:50], dtype, "two requests in one step: the first", mg[:50])
+    close(got[50:], BU.plain_logits(folder, other), dtype, "two requests in one step: the second", BU.router_margins(folder, other))
+    r.cache.close(a)
+    r.cache.close(b)
