@@ -487,6 +487,7 @@ def bifusun_kernels(width: int, heads: int, kv_heads: int, head_dim: int, ff: in
     C = cq + ck + cv
     taps = 4
     conv, bias = rand(C, taps, dtype=torch.float32), rand(C, dtype=torch.float32)
+    conv_t = conv.t().contiguous()
     cos = torch.ones(8192, D // 2, device=dev)
     ones = torch.ones(D, device=dev)
     tails = torch.zeros(B + 1, C * (taps - 1), device=dev)
@@ -502,7 +503,7 @@ def bifusun_kernels(width: int, heads: int, kv_heads: int, head_dim: int, ff: in
         ms = _time_ms(lambda: ops.qk_norm_rope_store(qkv, ones, ones, cos, cos, pos, slots, k_pool, v_pool, H, KV, D, 1e-6, status), flush=flush)
         put(f"qk_norm_rope_store {name}", None, ms, bytes_=n * C * 2 * 2)
         state_slots = i32(list(range(len(q_lens))))
-        ms = _time_ms(lambda: ops.conv_qkv_store(qkv, cq, ck, cv, conv=conv, bias=bias, tails=tails, k_pool=k_pool, v_pool=v_pool, slots=slots,
+        ms = _time_ms(lambda: ops.conv_qkv_store(qkv, cq, ck, cv, conv=conv, conv_t=conv_t, bias=bias, tails=tails, k_pool=k_pool, v_pool=v_pool, slots=slots,
                                                  req_of_token=req, cu_q=cu, state_slots=state_slots, positions=pos, n_requests=len(q_lens),
                                                  status=status, temp_coef=0.5, temp_every=128, blend=lam, first=first,
                                                  single_tokens=len(q_lens) > 1), flush=flush)

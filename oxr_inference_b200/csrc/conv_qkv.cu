@@ -65,25 +65,34 @@ __global__ void conv_qkv_store_kernel(
 
 
 // The same for bfloat16 with 16-byte accesses: a thread takes 8 neighbouring channels (all of q, of k or of v: the three widths are
-// multiples of 8). ROLL: every request brings exactly one token (a decode step), so the thread that filters a channel is the only one
+// multiples of 8). Its filter comes transposed, wt [taps, channels], so that a thread's 8 weights of a tap are 32 contiguous bytes and a
+// warp's are one run (read from [channels, taps], every load of a warp touched 32 lines, and the kernel was slower than the scalar one). ROLL: every request brings exactly one token (a decode step), so the thread that filters a channel is the only one
 // that reads its tail and rolls it forward itself; otherwise the roll kernel follows.
 struct __align__(16) Bf16x8 { __nv_bfloat162 v[4]; };
 
 template <bool ROLL>
 __global__ void conv_qkv_store_bf16x8_kernel(
     __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ v_out, const __nv_bfloat16* __restrict__ proj, int proj_stride, int cq, int ck,
-    int cv, int taps, const float* __restrict__ w, const float* __restrict__ bias, float* __restrict__ tails, long long slot_stride,
+    int cv, int taps, const float* __restrict__ wt, const float* __restrict__ bias, float* __restrict__ tails, long long slot_stride,
     const int* __restrict__ req_of_token, const int* __restrict__ cu_q, const int* __restrict__ state_slots, const int* __restrict__ positions,
     float temp_coef, int temp_every, const float* __restrict__ blend, const __nv_bfloat16* __restrict__ first, __nv_bfloat16* __restrict__ k_pool,
     __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ slots, long long n_slots, int* status) {
     const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
     const int t = blockIdx.x;
-    if (c >= cq + ck + cv) return;
+    const int channels = cq + ck + cv;
+    if (c >= channels) return;
     const int r = ROLL ? t : req_of_token[t];
     const int i = ROLL ? 0 : t - cu_q[r];
-    float b[8], acc[8], cur[8];
+    float b[8], acc[8], cur[8], wj[8];
+    auto load8f = [&](const float* src, float* out) {      // 8 floats from a 32-byte aligned run
+        const float4 lo = *reinterpret_cast<const float4*>(src), hi = *reinterpret_cast<const float4*>(src + 4);
+        out[0] = lo.x; out[1] = lo.y; out[2] = lo.z; out[3] = lo.w;
+        out[4] = hi.x; out[5] = hi.y; out[6] = hi.z; out[7] = hi.w;
+    };
+    if (bias != nullptr) load8f(bias + c, b);
+    else
 #pragma unroll
-    for (int k = 0; k < 8; ++k) b[k] = bias != nullptr ? bias[c + k] : 0.f;
+        for (int k = 0; k < 8; ++k) b[k] = 0.f;
     auto load8 = [&](int row, float* out) {
         const Bf16x8 raw = *reinterpret_cast<const Bf16x8*>(proj + (size_t)row * proj_stride + c);
 #pragma unroll
@@ -99,8 +108,9 @@ __global__ void conv_qkv_store_bf16x8_kernel(
 #pragma unroll
         for (int k = 0; k < 8; ++k) acc[k] = cur[k];
     } else {
+        load8f(wt + (size_t)(taps - 1) * channels + c, wj);
 #pragma unroll
-        for (int k = 0; k < 8; ++k) acc[k] = w[(c + k) * taps + taps - 1] * cur[k];
+        for (int k = 0; k < 8; ++k) acc[k] = wj[k] * cur[k];
         for (int j = 0; j < taps - 1; ++j) {
             const int back = taps - 1 - j;
             float u[8];
@@ -110,8 +120,9 @@ __global__ void conv_qkv_store_bf16x8_kernel(
 #pragma unroll
                 for (int k = 0; k < 8; ++k) u[k] = tail[k * (taps - 1) + taps - 1 + (i - back)];
             }
+            load8f(wt + (size_t)j * channels + c, wj);
 #pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] = fmaf(w[(c + k) * taps + j], u[k], acc[k]);
+            for (int k = 0; k < 8; ++k) acc[k] = fmaf(wj[k], u[k], acc[k]);
         }
         if (ROLL && taps > 1) {
             for (int k = 0; k < 8; ++k) {
@@ -177,7 +188,7 @@ __global__ void conv_qkv_roll_kernel(float* __restrict__ tails, long long slot_s
 }
 
 OXR_API int oxr_conv_qkv_store(void* q_out, void* v_out, const void* proj, int n_tokens, int n_requests, int proj_stride, int cq, int ck, int cv,
-                               int taps, const float* w, const float* bias, float* tails, long long slot_stride, const int* req_of_token,
+                               int taps, const float* w, const float* wt, const float* bias, float* tails, long long slot_stride, const int* req_of_token,
                                const int* cu_q, const int* state_slots, const int* positions, float temp_coef, int temp_every,
                                const float* blend, const void* first, void* k_pool, void* v_pool, const int* slots, long long n_slots, int dtype,
                                int single_tokens, int* status, cudaStream_t stream) {
@@ -200,12 +211,12 @@ OXR_API int oxr_conv_qkv_store(void* q_out, void* v_out, const void* proj, int n
     } while (0)
     const auto aligned = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
     if (dtype == 1 && cq % 8 == 0 && ck % 8 == 0 && cv % 8 == 0 && proj_stride % 8 == 0 && aligned(proj) && aligned(q_out) && aligned(v_out) &&
-        aligned(first) && aligned(k_pool) && aligned(v_pool)) {
+        aligned(first) && aligned(k_pool) && aligned(v_pool) && (taps == 0 || wt != nullptr) && aligned(wt) && aligned(bias)) {
         using B = __nv_bfloat16;
         dim3 vgrid(n_tokens, (channels / 8 + threads - 1) / threads);
         const bool single = n_tokens == n_requests && single_tokens;
 #define OXR_CONV_QKV8(ROLL) \
-        conv_qkv_store_bf16x8_kernel<ROLL><<<vgrid, threads, 0, stream>>>((B*)q_out, (B*)v_out, (const B*)proj, proj_stride, cq, ck, cv, taps, w, bias, \
+        conv_qkv_store_bf16x8_kernel<ROLL><<<vgrid, threads, 0, stream>>>((B*)q_out, (B*)v_out, (const B*)proj, proj_stride, cq, ck, cv, taps, wt, bias, \
                                                                          tails, slot_stride, req_of_token, cu_q, state_slots, positions, temp_coef, \
                                                                          temp_every, blend, (const B*)first, (B*)k_pool, (B*)v_pool, slots, n_slots, status)
         if (single) {

@@ -92,10 +92,35 @@ __global__ void gated_relu2_kernel(T* __restrict__ a, const T* __restrict__ u, c
     a[i] = Num<T>::from_f32(g * (v * v));
 }
 
+// the same for bfloat16 with 16-byte accesses: 8 neighbouring columns of one expert (ff a multiple of 8)
+__global__ void gated_relu2_bf16x8_kernel(__nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ u, const float* __restrict__ gate,
+                                          size_t total8, int cols, int ff, int E) {
+    const size_t i8 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i8 >= total8) return;
+    const size_t i = i8 * 8, t = i / cols;
+    const int c = (int)(i - t * cols);
+    const float g = gate != nullptr ? gate[t * E + c / ff] : 1.f;
+    uint4 raw = *reinterpret_cast<const uint4*>(u + i);
+    __nv_bfloat162* p = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        float2 f = __bfloat1622float2(p[k]);
+        f.x = fmaxf(f.x, 0.f);
+        f.y = fmaxf(f.y, 0.f);
+        p[k] = __floats2bfloat162_rn(g * (f.x * f.x), g * (f.y * f.y));
+    }
+    *reinterpret_cast<uint4*>(a + i) = raw;
+}
+
 OXR_API int oxr_gated_relu2(void* a, const void* u, const float* gate, int n_tokens, int E, int ff, int dtype, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (E <= 0 || ff <= 0) return OXR_BAD_ARGUMENT;
     const size_t total = (size_t)n_tokens * E * ff;
+    if (dtype == 1 && ff % 8 == 0 && (uintptr_t)a % 16 == 0 && (uintptr_t)u % 16 == 0) {
+        gated_relu2_bf16x8_kernel<<<(unsigned)((total / 8 + 255) / 256), 256, 0, stream>>>((__nv_bfloat16*)a, (const __nv_bfloat16*)u, gate, total / 8,
+                                                                                            E * ff, ff, E);
+        return oxr_launch_status();
+    }
     const unsigned blocks = (unsigned)((total + 255) / 256);
     if (dtype == 0) gated_relu2_kernel<float><<<blocks, 256, 0, stream>>>((float*)a, (const float*)u, gate, total, E * ff, ff, E);
     else gated_relu2_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)a, (const __nv_bfloat16*)u, gate, total, E * ff, ff, E);
@@ -109,9 +134,11 @@ OXR_API int oxr_gated_relu2(void* a, const void* u, const float* gate, int n_tok
 constexpr int SORT_MAX_EXPERTS = 1024;
 
 __global__ void __launch_bounds__(1024) expert_sort_kernel(int* __restrict__ counts, int* __restrict__ order, int* __restrict__ place,
-                                                          const int* __restrict__ ids, int total, int E) {
+                                                          int* __restrict__ tile_group, const int* __restrict__ ids, int total, int E, int pad,
+                                                          int capacity) {
     __shared__ int hist[SORT_MAX_EXPERTS], cursor[SORT_MAX_EXPERTS];
     for (int e = threadIdx.x; e < E; e += blockDim.x) hist[e] = 0;
+    for (int i = threadIdx.x; i < capacity; i += blockDim.x) order[i] = -1;
     __syncthreads();
     for (int i = threadIdx.x; i < total; i += blockDim.x) {
         const int e = ids[i];
@@ -123,8 +150,13 @@ __global__ void __launch_bounds__(1024) expert_sort_kernel(int* __restrict__ cou
         for (int e = 0; e < E; ++e) {
             cursor[e] = at;
             counts[e] = hist[e];
-            at += hist[e];
+            const int end = at + (hist[e] + pad - 1) / pad * pad;      // every expert's stretch is padded to whole tiles of `pad` rows
+            if (tile_group != nullptr)
+                for (int tile = at / pad; tile < end / pad; ++tile) tile_group[tile] = e;
+            at = end;
         }
+        if (tile_group != nullptr)
+            for (int tile = at / pad; tile < capacity / pad; ++tile) tile_group[tile] = -1;   // tiles nobody uses
     }
     __syncthreads();
     for (int i = threadIdx.x; i < total; i += blockDim.x) {
@@ -139,17 +171,25 @@ __global__ void __launch_bounds__(1024) expert_sort_kernel(int* __restrict__ cou
     }
 }
 
-OXR_API int oxr_expert_sort(int* counts, int* order, int* place, const int* ids, int total, int E, cudaStream_t stream) {
+// pad: every expert's stretch of the ordered list starts at a multiple of `pad` (places in between hold -1); capacity: length of `order`,
+// at least total + E * (pad - 1) rounded up to a multiple of pad; tile_group (optional): which expert each tile of `pad` places belongs to.
+OXR_API int oxr_expert_sort(int* counts, int* order, int* place, int* tile_group, const int* ids, int total, int E, int pad, int capacity,
+                            cudaStream_t stream) {
     if (total <= 0) return 0;
-    if (E <= 0 || E > SORT_MAX_EXPERTS) return OXR_BAD_ARGUMENT;
-    expert_sort_kernel<<<1, 1024, 0, stream>>>(counts, order, place, ids, total, E);
+    if (E <= 0 || E > SORT_MAX_EXPERTS || pad <= 0 || capacity % pad != 0 || capacity < total + (pad > 1 ? E * (pad - 1) : 0)) return OXR_BAD_ARGUMENT;
+    expert_sort_kernel<<<1, 1024, 0, stream>>>(counts, order, place, tile_group, ids, total, E, pad, capacity);
     return oxr_launch_status();
 }
 
-// out[i] = x[order[i] / per_row]: 16-byte copies where the rows allow them
+// out[i] = x[order[i] / per_row] (zeros where order[i] is -1): 16-byte copies where the rows allow them
 template <typename T>
 __global__ void gather_rows_kernel(T* __restrict__ out, const T* __restrict__ x, const int* __restrict__ order, int width, int per_row) {
-    const size_t dst = (size_t)blockIdx.x * width, src = (size_t)(order[blockIdx.x] / per_row) * width;
+    const int from = order[blockIdx.x];          // -1: a padding place, filled with zeros
+    const size_t dst = (size_t)blockIdx.x * width, src = (size_t)(from < 0 ? 0 : from / per_row) * width;
+    if (from < 0) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) out[dst + i] = Num<T>::from_f32(0.f);
+        return;
+    }
     const bool wide = (width * sizeof(T)) % 16 == 0 && ((uintptr_t)out & 15) == 0 && ((uintptr_t)x & 15) == 0;
     if (wide) {
         const int4* s4 = reinterpret_cast<const int4*>(x + src);

@@ -64,7 +64,9 @@ template <typename TO, bool SPLIT, bool GATED>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_w,
                     int M, int N, int K, int bn, int stages, int tmem_cols, int num_tiles, int splits, float* __restrict__ partial,
-                    unsigned int* __restrict__ tickets, int* status, const GateForm gate) {
+                    unsigned int* __restrict__ tickets, int* status, const GateForm gate, const int* __restrict__ tile_group) {
+    // tile_group (optional): W stacks several matrices of N rows each, and the 128 rows of X from m0 on multiply matrix
+    // tile_group[m0 / 128] (rows grouped by the matrix they belong to, each group padded to whole tiles of rows).
     static_assert(!(GATED && SPLIT), "the gated epilogue is the plain one's variant only");
     extern __shared__ unsigned char smem_raw[];
     unsigned char* tiles = reinterpret_cast<unsigned char*>(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);   // swizzle atoms are 1024 B
@@ -109,7 +111,7 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
             // (when it is launched dependent on the one before) waits for that one to finish; the activations' tiles
             // of the same stages follow after the wait.
             int early = 0;
-            for (int unit = blockIdx.x; unit < num_units && early < stages; unit += gridDim.x) {
+            for (int unit = blockIdx.x; unit < num_units && early < stages && tile_group == nullptr; unit += gridDim.x) {
                 const int tile = SPLIT ? unit / splits : unit;
                 int m0, n0;
                 tile_origin(tile, M, N, bn, m0, n0);
@@ -125,6 +127,9 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
                 const int tile = SPLIT ? unit / splits : unit;
                 int m0, n0;
                 tile_origin(tile, M, N, bn, m0, n0);
+                const int group = tile_group == nullptr ? 0 : tile_group[m0 / BM];   // read after the wait: a kernel before wrote it
+                if (group < 0) continue;   // a tile of rows that belongs to no group: all three roles skip it
+                const int w_row = n0 + group * N;
                 for (int kb = SPLIT ? unit % splits : 0; kb < num_kb; kb += kb_step, ++step) {
                     unsigned char* a_dst = tiles + (size_t)s * stage_size;
                     if (step < early) {   // first ring: the stage is free and armed, its weight tile is on its way
@@ -133,7 +138,7 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
                         if (!mbar_wait(empty + s, phase ^ 1)) { atomicExch(gave_up, 1u); oxr_report(status, OXR_WAIT_EXPIRED, 0); ok = false; break; }
                         mbar_expect_tx(full + s, (uint32_t)stage_size);
                         tma_load_2d(a_dst, &map_x, kb * BK, m0, full + s);
-                        tma_load_2d(a_dst + A_BYTES, &map_w, kb * BK, n0, full + s);
+                        tma_load_2d(a_dst + A_BYTES, &map_w, kb * BK, w_row, full + s);
                     }
                     if (++s == stages) { s = 0; phase ^= 1; }
                 }
@@ -148,7 +153,12 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
             uint32_t phase = 0;
             bool ok = true;
             int it = 0;
-            for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x, ++it) {
+            for (int unit = blockIdx.x; unit < num_units && ok; unit += gridDim.x) {
+                if (tile_group != nullptr) {
+                    int m0, n0;
+                    tile_origin(unit, M, N, bn, m0, n0);
+                    if (tile_group[m0 / BM] < 0) continue;
+                }
                 const int kb0 = SPLIT ? unit % splits : 0;
                 const int acc = it & 1;
                 const uint32_t acc_phase = (it >> 1) & 1;
@@ -170,6 +180,7 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
                     if (++s == stages) { s = 0; phase ^= 1; }
                 }
                 umma_commit(accum_full + acc);   // arrives when every MMA issued so far is complete (also after giving up)
+                ++it;
             }
         }
     } else {
@@ -177,10 +188,11 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
         pdl_wait();   // C and the workspace may still be read by the kernels before this one
         const int quarter = warp & 3;                     // this warp may touch TMEM lanes 32 * quarter .. + 31
         int it = 0;
-        for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x, ++it) {
+        for (int unit = blockIdx.x; unit < num_units; unit += gridDim.x) {
             const int tile = SPLIT ? unit / splits : unit;
             int m0, n0;
             tile_origin(tile, M, N, bn, m0, n0);
+            if (tile_group != nullptr && tile_group[m0 / BM] < 0) continue;
             const int acc = it & 1;
             const uint32_t acc_phase = (it >> 1) & 1;
             const int row = m0 + quarter * 32 + lane;
@@ -208,7 +220,16 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
                             if (4 * j < count) reinterpret_cast<uint4*>(mine + c0)[j] = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                     } else if (n0 + c0 < N) {
                         if constexpr (GATED) store_row_piece_gated<TO>(C + (size_t)row * (N / 2) + (n0 + c0) / 2, v, count, n0 + c0, N, gate);
-                        else store_row_piece<TO>(C + (size_t)row * N + n0 + c0, v, count, n0 + c0, N);
+                        else {
+                            if (gate.kind == 2) {   // the plain product's optional activation: relu(x)^2 of the fp32 sums
+#pragma unroll
+                                for (int j = 0; j < 32; ++j) {
+                                    const float f = fmaxf(__uint_as_float(v[j]), 0.f);
+                                    v[j] = __float_as_uint(f * f);
+                                }
+                            }
+                            store_row_piece<TO>(C + (size_t)row * N + n0 + c0, v, count, n0 + c0, N);
+                        }
                     }
                 }
             }
@@ -274,6 +295,7 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
                     }
                 }
             }
+            ++it;
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -287,7 +309,7 @@ gemm_tcgen05_kernel(TO* __restrict__ C, const __grid_constant__ CUtensorMap map_
 // ---------------------------------------------------------------------------------------------------- host side
 template <typename TO, bool SPLIT, bool GATED = false>
 int launch(void* C, const void* X, const void* W, int M, int N, int K, int bn, int splits, float* partial, unsigned int* tickets, int* status,
-           cudaStream_t stream) {
+           cudaStream_t stream, int groups = 1, const int* tile_group = nullptr, int act = 0) {
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<TO, SPLIT, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -295,7 +317,7 @@ int launch(void* C, const void* X, const void* W, int M, int N, int K, int bn, i
         configured = true;
     }
     CUtensorMap map_x, map_w;
-    if (!oxr_make_map_bf16(&map_x, X, M, K, BM) || !oxr_make_map_bf16(&map_w, W, N, K, bn)) return OXR_BAD_ARGUMENT;
+    if (!oxr_make_map_bf16(&map_x, X, M, K, BM) || !oxr_make_map_bf16(&map_w, W, (unsigned long long)N * groups, K, bn)) return OXR_BAD_ARGUMENT;
     const long long tiles = (long long)((N + bn - 1) / bn) * ((M + BM - 1) / BM);
     const long long units = tiles * (SPLIT ? splits : 1);
     if (units > 0x7fffffffLL) return OXR_BAD_ARGUMENT;
@@ -311,7 +333,8 @@ int launch(void* C, const void* X, const void* W, int M, int N, int K, int bn, i
     while (tmem_cols < 2 * bn) tmem_cols *= 2;
     dim3 grid((unsigned)(units < num_sms ? units : num_sms));   // one block per SM (its shared memory fills the SM)
     oxr_launch(gemm_tcgen05_kernel<TO, SPLIT, GATED>, grid, dim3(TC_THREADS), SMEM_BYTES, stream, true, (TO*)C, map_x, map_w, M, N, K, bn,
-               stages, tmem_cols, (int)tiles, splits, partial, tickets, status, oxr_gate_form);
+               stages, tmem_cols, (int)tiles, splits, partial, tickets, status, act == 1 ? GateForm{2, 0.f, 0.f} : (GATED ? oxr_gate_form : GateForm{0, 1.f, 0.f}),
+               tile_group);
     return oxr_launch_status();
 }
 }  // namespace
@@ -334,6 +357,20 @@ OXR_API int oxr_gemm_tcgen05_bf16(void* C, const void* X, const void* W, int M, 
     }
     if (out_dtype == 1) return launch<__nv_bfloat16, false>(C, X, W, M, N, K, tile_n, 1, nullptr, nullptr, status, stream);
     if (out_dtype == 0) return launch<float, false>(C, X, W, M, N, K, tile_n, 1, nullptr, nullptr, status, stream);
+    return OXR_BAD_ARGUMENT;
+}
+
+// Rows grouped by matrix: W [groups * N, K] stacks `groups` matrices, M is a multiple of 128, and the rows m0 .. m0 + 127 of X are
+// multiplied by matrix tile_group[m0 / 128] (a device array of M / 128 entries in 0 .. groups - 1; -1: the tile belongs to no group and is
+// not computed, its rows of C are left as they are). act 1: the output is relu(x)^2 of the fp32 sums. No shares of k.
+OXR_API int oxr_gemm_tcgen05_grouped_bf16(void* C, const void* X, const void* W, int M, int N, int K, int groups, const int* tile_group,
+                                          int out_dtype, int tile_n, int act, int* status, cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || K % 8 != 0 || (uintptr_t)X % 16 != 0 || (uintptr_t)W % 16 != 0 || M % BM != 0 || groups <= 0 || tile_group == nullptr)
+        return OXR_BAD_ARGUMENT;
+    if (tile_n < 16 || tile_n > MAX_BN || tile_n % 16 != 0) return OXR_BAD_ARGUMENT;
+    if (out_dtype == 1) return launch<__nv_bfloat16, false>(C, X, W, M, N, K, tile_n, 1, nullptr, nullptr, status, stream, groups, tile_group, act);
+    if (out_dtype == 0) return launch<float, false>(C, X, W, M, N, K, tile_n, 1, nullptr, nullptr, status, stream, groups, tile_group, act);
     return OXR_BAD_ARGUMENT;
 }
 

@@ -138,20 +138,21 @@ def _lib():
         lib.oxr_scatter_rows.argtypes = [p, ll, ll, p, i, i, i, p, i, i, p, p, ll, i, p]
         lib.oxr_latent_prep.argtypes = [p, ll, ll, p, i, i, p, f, p, i, i, i, p, i, i, p, p, i, p, i, i, p, p]
         lib.oxr_head_linear.argtypes = [p, i, i, p, i, i, p, i, i, i, i, i, p]
-        lib.oxr_conv_qkv_store.argtypes = [p, p, p, i, i, i, i, i, i, i, p, p, p, ll, p, p, p, p, f, i, p, p, p, p, p, ll, i, i, p, p]
+        lib.oxr_conv_qkv_store.argtypes = [p, p, p, i, i, i, i, i, i, i, p, p, p, p, ll, p, p, p, p, f, i, p, p, p, p, p, ll, i, i, p, p]
         lib.oxr_add_bias.argtypes = [p, p, i, i, i, p]
         lib.oxr_scale_f32.argtypes = [p, f, ll, p]
         lib.oxr_mlstm_scan.argtypes = [p, p, p, i, i, i, i, i, p, p, i, i, i, f, f, p, ll, p, p, i, p]
         lib.oxr_head_norm_gate.argtypes = [p, p, p, i, i, i, p, i, i, f, i, p]
         lib.oxr_route.argtypes = [p, p, p, p, i, i, i, i, i, f, p]
         lib.oxr_gated_relu2.argtypes = [p, p, p, i, i, i, i, p]
-        lib.oxr_expert_sort.argtypes = [p, p, p, p, i, i, p]
+        lib.oxr_expert_sort.argtypes = [p, p, p, p, p, i, i, i, i, p]
+        lib.oxr_gemm_tcgen05_grouped_bf16.argtypes = [p, p, p, i, i, i, i, p, i, i, i, p, p]
         lib.oxr_gather_rows.argtypes = [p, p, p, i, i, i, i, p]
         lib.oxr_combine_rows.argtypes = [p, p, p, p, i, i, i, i, p]
         for name in ("oxr_stream_rms_norm", "oxr_norm_add_norm", "oxr_concat2_cast", "oxr_add_row_f32", "oxr_clamped_glu", "oxr_rotary_angles",
                      "oxr_mamba_conv", "oxr_mamba_scan", "oxr_gated_group_norm", "oxr_attention_rows", "oxr_scatter_rows", "oxr_latent_prep",
                      "oxr_head_linear", "oxr_conv_qkv_store", "oxr_add_bias", "oxr_scale_f32", "oxr_mlstm_scan", "oxr_head_norm_gate", "oxr_route",
-                     "oxr_gated_relu2", "oxr_expert_sort", "oxr_gather_rows", "oxr_combine_rows"):
+                     "oxr_gated_relu2", "oxr_expert_sort", "oxr_gather_rows", "oxr_combine_rows", "oxr_gemm_tcgen05_grouped_bf16"):
             getattr(lib, name).restype = c_int
         for name in ("oxr_embedding", "oxr_add_rms_norm", "oxr_silu_mul", "oxr_cast", "oxr_qk_norm_rope_store",
                      "oxr_gemm_f32_nt", "oxr_gemm_skinny_bf16", "oxr_gemm_skinny_gated_bf16", "oxr_gemm_stream_bf16", "oxr_gemm_stream_gated_bf16", "oxr_gemm_tcgen05_bf16", "oxr_gemm_tcgen05_pair_bf16", "oxr_gemm_tcgen05_gated_bf16", "oxr_gemm_few_rows_cluster_bf16", "oxr_gemm_few_rows_max_clusters",
@@ -1256,13 +1257,14 @@ def conv_qkv_store(proj: torch.Tensor, cq: int, ck: int, cv: int, *, conv: torch
                    k_pool: torch.Tensor, v_pool: torch.Tensor, slots: torch.Tensor, req_of_token: torch.Tensor, cu_q: torch.Tensor,
                    state_slots: torch.Tensor, positions: torch.Tensor, n_requests: int, status: torch.Tensor, temp_coef: float = 0.0,
                    temp_every: int = 0, blend: torch.Tensor | None = None, first: torch.Tensor | None = None, keep_values: bool = False,
-                   single_tokens: bool = False) -> tuple[torch.Tensor, torch.Tensor | None]:
+                   single_tokens: bool = False, conv_t: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:
     """From a packed step's stacked projection ``proj [tokens, >= cq + ck + cv]`` to queries and cache rows in one launch (and one more that
     rolls the tails): add ``bias [cq + ck + cv]``, filter every channel causally with ``conv [channels, taps]`` (the last tap meets the current
     token; what stands before a step's first token comes from the request's ``tails`` row ``[channels, taps - 1]``, zero for a new request,
     which is rolled forward), multiply the queries by ``1 + temp_coef ln(floor((p + 1) / temp_every) + 1)`` (``temp_every`` 0: not), blend the
     values as ``(1 - blend) v + blend first`` (``blend``: one fp32 number on the device; ``first [tokens, cv]``), and write keys and values to
-    ``k_pool`` / ``v_pool`` (one layer's ``[pages, page_size, KV, D]``) at ``slots`` (-1 skips). ``conv`` None: no filter. ``single_tokens``: the
+    ``k_pool`` / ``v_pool`` (one layer's ``[pages, page_size, KV, D]``) at ``slots`` (-1 skips). ``conv`` None: no filter. ``conv_t``: the same filter
+    transposed, ``[taps, channels]``, which the 16-byte bfloat16 kernel reads (without it the scalar kernel runs). ``single_tokens``: the
     caller knows that every request brings exactly one token (token r is request r's); the bfloat16 kernel then rolls the tails itself.
     Returns the queries ``[tokens, cq]`` and, with ``keep_values``, the values ``[tokens, cv]`` as they were cached."""
     _need(proj, "proj")
@@ -1275,6 +1277,10 @@ def conv_qkv_store(proj: torch.Tensor, cq: int, ck: int, cv: int, *, conv: torch
         if conv.shape[0] != channels:
             raise KernelError(f"conv_qkv_store: the filter has {conv.shape[0]} channels for {channels}")
         taps = conv.shape[1]
+        if conv_t is not None:
+            _need(conv_t, "conv_t", torch.float32)
+            if conv_t.shape != (taps, channels):
+                raise KernelError("conv_qkv_store: the transposed filter must be [taps, channels]")
     if bias is not None:
         _need(bias, "bias", torch.float32)
         if bias.numel() != channels:
@@ -1291,13 +1297,13 @@ def conv_qkv_store(proj: torch.Tensor, cq: int, ck: int, cv: int, *, conv: torch
             raise KernelError("conv_qkv_store: the values to blend with must be [tokens, cv]")
     q = torch.empty((n, cq), dtype=proj.dtype, device=proj.device)
     v = torch.empty((n, cv), dtype=proj.dtype, device=proj.device) if keep_values else None
-    _done(_lib().oxr_conv_qkv_store(q.data_ptr(), _ptr(v), proj.data_ptr(), n, n_requests, proj.shape[1], cq, ck, cv, taps, _ptr(conv), _ptr(bias),
+    _done(_lib().oxr_conv_qkv_store(q.data_ptr(), _ptr(v), proj.data_ptr(), n, n_requests, proj.shape[1], cq, ck, cv, taps, _ptr(conv), _ptr(conv_t) if conv is not None else None, _ptr(bias),
                                     _ptr(tails), tails.stride(0) if tails is not None else 0, req_of_token.data_ptr(), cu_q.data_ptr(),
                                     state_slots.data_ptr(), positions.data_ptr(), float(temp_coef), int(temp_every), _ptr(blend), _ptr(first),
                                     k_pool.data_ptr(), v_pool.data_ptr(), slots.data_ptr(), k_pool.shape[0] * k_pool.shape[1], _dtype_code(proj),
                                     int(bool(single_tokens) and n == n_requests), status.data_ptr(), _stream()), "conv_qkv_store")
     global launch_count
-    launch_count += 1 if taps > 1 and not (single_tokens and n == n_requests and proj.dtype == torch.bfloat16) else 0
+    launch_count += 1 if taps > 1 and not (single_tokens and n == n_requests and proj.dtype == torch.bfloat16 and conv_t is not None) else 0
     return q, v
 
 
@@ -1392,16 +1398,50 @@ def gated_relu2(u: torch.Tensor, gate: torch.Tensor | None, ff: int, out: torch.
     return a
 
 
-def expert_sort(ids: torch.Tensor, experts: int) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """The (token, choice) pairs of ``ids [tokens, top]`` ordered by expert: ``counts [experts]`` (int32), ``order [tokens * top]`` (the flat pair
-    index at each place of the ordered list) and ``place [tokens * top]`` (its inverse). Pairs of one expert stand in no particular order."""
+GROUP_TILE_ROWS = 128
+"""Rows per tile of the grouped product: every group's rows are padded to a multiple of it."""
+
+
+def expert_sort(ids: torch.Tensor, experts: int, pad: int = 1) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor | None]:
+    """The (token, choice) pairs of ``ids [tokens, top]`` ordered by expert: ``counts [experts]`` (int32), ``order`` (the flat pair index at each
+    place of the ordered list, -1 at padding places) and ``place [tokens * top]`` (where each pair stands in the list). Pairs of one expert stand
+    in no particular order. ``pad`` > 1: every expert's stretch starts at a multiple of ``pad``; the list then has room for the worst case
+    (``tokens * top + experts * (pad - 1)``, rounded up), and the fourth result says which expert each tile of ``pad`` places belongs to."""
     _need(ids, "ids", torch.int32)
     total = ids.numel()
+    capacity = total if pad <= 1 else -(-(total + experts * (pad - 1)) // pad) * pad
     counts = torch.empty(experts, dtype=torch.int32, device=ids.device)
-    order = torch.empty(total, dtype=torch.int32, device=ids.device)
+    order = torch.empty(capacity, dtype=torch.int32, device=ids.device)
     place = torch.empty(total, dtype=torch.int32, device=ids.device)
-    _done(_lib().oxr_expert_sort(counts.data_ptr(), order.data_ptr(), place.data_ptr(), ids.data_ptr(), total, int(experts), _stream()), "expert_sort")
-    return counts, order, place
+    tile_group = torch.empty(capacity // pad, dtype=torch.int32, device=ids.device) if pad > 1 else None
+    _done(_lib().oxr_expert_sort(counts.data_ptr(), order.data_ptr(), place.data_ptr(), _ptr(tile_group), ids.data_ptr(), total, int(experts), int(pad),
+                                 capacity, _stream()), "expert_sort")
+    return counts, order, place, tile_group
+
+
+def grouped_linear_takes(x_dtype: torch.dtype, weight: torch.Tensor, k: int) -> bool:
+    """Whether :func:`grouped_linear` serves these operands: bfloat16 with rows of whole 16-byte words."""
+    return x_dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and k % 8 == 0 and weight.data_ptr() % 16 == 0
+
+
+def grouped_linear(x: torch.Tensor, weight: torch.Tensor, tile_group: torch.Tensor, n: int, out_dtype: torch.dtype | None = None,
+                   relu2: bool = False) -> torch.Tensor:
+    """``out[r] = x[r] @ weight[g n : (g + 1) n].T`` with ``g = tile_group[r // GROUP_TILE_ROWS]``: rows ordered by the matrix they multiply (each
+    group padded to whole tiles of rows), ``weight [groups * n, k]`` the matrices stacked. One launch of the TMA + tcgen05 kernel, whatever
+    the groups' sizes, which stay on the device. A tile whose group is -1 is not computed (its rows of ``out`` are zero). ``relu2``: the
+    epilogue writes ``relu(out)^2`` of the fp32 sums."""
+    _need(x, "x", torch.bfloat16)
+    _need(weight, "weight", torch.bfloat16)
+    _need(tile_group, "tile_group", torch.int32)
+    m, k = x.shape
+    if weight.shape[1] != k or weight.shape[0] % n or m % GROUP_TILE_ROWS or tile_group.numel() != m // GROUP_TILE_ROWS or k % 8:
+        raise KernelError("grouped_linear: sizes do not fit")
+    out_dtype = out_dtype or x.dtype
+    out = torch.zeros((m, n), dtype=out_dtype, device=x.device)
+    tile_n, _ = _gemm_plan(m, n, k, False)
+    _done(_lib().oxr_gemm_tcgen05_grouped_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, weight.shape[0] // n, tile_group.data_ptr(),
+                                               _DT[out_dtype], tile_n, int(relu2), new_status(x.device).data_ptr(), _stream()), "gemm_tcgen05_grouped")
+    return out
 
 
 def gather_rows(x: torch.Tensor, order: torch.Tensor, per_row: int) -> torch.Tensor:
@@ -1415,12 +1455,12 @@ def gather_rows(x: torch.Tensor, order: torch.Tensor, per_row: int) -> torch.Ten
 
 
 def combine_rows(y: torch.Tensor, place: torch.Tensor, weights: torch.Tensor) -> torch.Tensor:
-    """``out[t] = sum_j weights[t, j] * y[place[t * top + j]]`` with the sum in fp32 in the order of j; ``y [tokens * top, width]``."""
+    """``out[t] = sum_j weights[t, j] * y[place[t * top + j]]`` with the sum in fp32 in the order of j; ``y [>= tokens * top, width]``."""
     _need(y, "y")
     _need(place, "place", torch.int32)
     _need(weights, "weights", torch.float32)
     n, top = weights.shape
-    if place.numel() != n * top or y.shape[0] != n * top:
+    if place.numel() != n * top or y.shape[0] < n * top:
         raise KernelError("combine_rows: sizes do not fit")
     out = torch.empty((n, y.shape[1]), dtype=y.dtype, device=y.device)
     _done(_lib().oxr_combine_rows(out.data_ptr(), y.data_ptr(), place.data_ptr(), weights.data_ptr(), n, top, y.shape[1], _dtype_code(y), _stream()),

@@ -21,8 +21,9 @@ class RoutedExperts(FeedForward):
     expert (zero when it was not chosen), and the sum over experts happens inside the second product's reduction. With a handful of tokens
     nearly every expert is chosen by someone, and the products are bound by reading the weights, which this form reads exactly once.
     From ``grouped_min_rows`` tokens on the work of the experts nobody chose would dominate, so the (token, choice) pairs are ordered by
-    expert on the device, the host reads how many each expert got (one synchronisation per layer), and every expert multiplies just its own
-    rows; a last kernel adds each token's ``top`` results with their weights in the order of the choices. Either way a token's result does
+    expert on the device and every expert multiplies just its own rows: in bfloat16 as one grouped product per projection (each expert's
+    rows padded to whole tiles, each tile with its own expert's matrix; no size comes back to the host), in 32-bit expert by expert after
+    the host has read the counts; a last kernel adds each token's ``top`` results with their weights in the order of the choices. Either way a token's result does
     not depend on what else is in the batch beyond rounding."""
 
     GROUPED_MIN_ROWS = 256
@@ -87,11 +88,19 @@ class RoutedExperts(FeedForward):
         if self.down_by_expert is None:
             # a second copy of the down-projections, expert by expert (the stacked one is laid out for the single product)
             self.down_by_expert = self.down.view(self.hidden, self.E, self.ff).permute(1, 0, 2).contiguous()
-        counts, order, place = ops.expert_sort(ids, self.E)
+        if ops.grouped_linear_takes(h.dtype, self.up, self.hidden) and ops.grouped_linear_takes(h.dtype, self.down_by_expert, self.ff):
+            # bfloat16: each expert's rows padded to whole tiles, then ONE product for all up-projections and one for all
+            # down-projections, each tile of rows with its own expert's matrix; nothing comes back to the host
+            _, order, place, tile_group = ops.expert_sort(ids, self.E, pad=ops.GROUP_TILE_ROWS)
+            x = ops.gather_rows(h, order, self.top)
+            a = ops.grouped_linear(x, self.up, tile_group, self.ff, relu2=True)     # the activation in the product's epilogue
+            y = ops.grouped_linear(a, self.down_by_expert.view(self.E * self.hidden, self.ff), tile_group, self.hidden)
+            return ops.combine_rows(y, place, weights)
+        counts, order, place, _ = ops.expert_sort(ids, self.E)
         x = ops.gather_rows(h, order, self.top)                  # [tokens * top, hidden], ordered by expert
         y = torch.empty((x.shape[0], self.hidden), dtype=x.dtype, device=x.device)
         at = 0
-        for e, c in enumerate(counts.tolist()):                  # the step's one synchronisation of this layer
+        for e, c in enumerate(counts.tolist()):                  # 32-bit and odd sizes: the host reads the counts (one synchronisation)
             if c:
                 u = ops.linear(x[at:at + c], self.up[e * self.ff:(e + 1) * self.ff])
                 ops.linear(ops.gated_relu2(u, None, self.ff, out=u), self.down_by_expert[e], out=y[at:at + c])

@@ -76,6 +76,7 @@ class MaskedAttention(Mixer):
         self.vectors: dict[str, torch.Tensor] = {}
         self.qkv_bias: torch.Tensor | None = None
         self.qkv_conv: torch.Tensor | None = None
+        self.qkv_conv_t: torch.Tensor | None = None
 
     @property
     def between(self) -> bool:
@@ -126,6 +127,7 @@ class MaskedAttention(Mixer):
             self.qkv_bias = torch.cat([v["q.b"], v["k.b"], v["v.b"]]).contiguous()
         if self.taps > 0:
             self.qkv_conv = torch.cat([v["q.conv"], v["k.conv"], v["v.conv"]]).contiguous()
+            self.qkv_conv_t = self.qkv_conv.t().contiguous()      # [taps, channels]: what the 16-byte kernel reads
         if self.value_mix is not None:
             v["vmix"] = v["vmix"].reshape(1)
 
@@ -168,7 +170,7 @@ class MaskedAttention(Mixer):
                     raise ValueError(f"no layer before this one kept its values under {self.value_mix_key!r}")
                 blend, first = self.vectors["vmix"], ctx.shared[self.value_mix_key]
             q, kept = ops.conv_qkv_store(
-                qkv, self.cq, self.ck, self.cv, conv=self.qkv_conv, bias=self.qkv_bias, tails=cache.state, k_pool=k_pool, v_pool=v_pool,
+                qkv, self.cq, self.ck, self.cv, conv=self.qkv_conv, conv_t=self.qkv_conv_t, bias=self.qkv_bias, tails=cache.state, k_pool=k_pool, v_pool=v_pool,
                 slots=group.slots if cache.store else ctx.no_store_slots, req_of_token=ctx.req_of_token, cu_q=ctx.cu_q,
                 state_slots=ctx.state_slots, positions=ctx.positions, n_requests=ctx.n_requests, status=ctx.status, temp_coef=self.temp_coef,
                 temp_every=self.temp_every, blend=blend, first=first, keep_values=self.value_mix == "keep", single_tokens=ctx.single_tokens)

@@ -260,19 +260,21 @@ def test_bfloat16_generation_with_graphs_equals_eager(tmp_path):
 
 
 # ------------------------------------------------------------------------------------------------ the kernels against their formulas
+@pytest.mark.parametrize("transposed", [False, True])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("taps", [0, 1, 2, 4])
-def test_filter_kernel_with_tails_across_steps(dtype, taps):
+def test_filter_kernel_with_tails_across_steps(dtype, taps, transposed):
     """Two requests whose tokens arrive in unequal portions (down to one token, fewer than the filter's taps): biases, filter,
-    temperature, blend, cache rows and the rolled tails against the formulas over the whole sequences."""
+    temperature, blend, cache rows and the rolled tails against the formulas over the whole sequences. With the filter also handed over
+    transposed, bfloat16 runs the 16-byte kernel."""
     from oxr_inference_b200 import ops
 
     g = torch.Generator().manual_seed(taps)
-    H, KV, DK, DV, P = 3, 1, 8, 12, 4
+    H, KV, DK, DV, P = 3, 1, 8, 16, 4
     cq, ck, cv = H * DK, KV * DK, KV * DV
     C = cq + ck + cv
     lens = [11, 7]
-    proj = [torch.randn(n, C + 5, generator=g).to(dtype) for n in lens]          # 5 columns that are not ours
+    proj = [torch.randn(n, C + 8, generator=g).to(dtype) for n in lens]          # 8 columns that are not ours
     first = [torch.randn(n, cv, generator=g).to(dtype) for n in lens]
     conv = torch.randn(C, taps, generator=g) if taps else None
     bias = torch.randn(C, generator=g)
@@ -293,7 +295,7 @@ def test_filter_kernel_with_tails_across_steps(dtype, taps):
     slot_of = [[(r * 4 + j // P) * P + j % P for j in range(n)] for r, n in enumerate(lens)]
     at = [0, 0]
     got_q = [[], []]
-    for cuts in ([1, 2], [3, 1], [1, 4], [2, 0], [4, 0]):
+    for cuts in ([1, 2], [3, 1], [1, 1], [1, 3], [1, 0], [4, 0]):     # with the transposed filter, steps of single tokens roll their tails inline
         rows, pos, req, cu, slots, firsts, order = [], [], [], [0], [], [], []
         for r, c in enumerate(cuts):
             if c == 0:
@@ -308,6 +310,7 @@ def test_filter_kernel_with_tails_across_steps(dtype, taps):
             at[r] += c
         i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
         q, kept = ops.conv_qkv_store(torch.cat(rows).to(DEV), cq, ck, cv, conv=None if conv is None else conv.to(DEV), bias=bias.to(DEV),
+                                     conv_t=None if conv is None or not transposed else conv.t().contiguous().to(DEV), single_tokens=max(cuts) == 1,
                                      tails=tails[:, :C * max(taps - 1, 0)] if taps > 1 else None, k_pool=k_pool, v_pool=v_pool, slots=i32(slots),
                                      req_of_token=i32(req), cu_q=i32(cu), state_slots=i32([2 - r for r, _ in order]), positions=i32(pos),
                                      n_requests=len(order), status=status, temp_coef=coef, temp_every=every,
@@ -431,12 +434,13 @@ def test_router_kernel(E, top, groups, keep):
     assert ((gate > 0).sum(1) == top).all()
 
 
+@pytest.mark.parametrize("ff", [12, 16])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_experts_activation(dtype):
+def test_experts_activation(dtype, ff):
     from oxr_inference_b200 import ops
 
     g = torch.Generator().manual_seed(3)
-    n, E, ff = 11, 5, 12
+    n, E = 11, 5
     u = torch.randn(n, E * ff, generator=g).to(dtype)
     gate = torch.rand(n, E, generator=g) * (torch.rand(n, E, generator=g) > 0.5)
     got = ops.gated_relu2(u.to(DEV), gate.to(DEV), ff).float().cpu()
@@ -612,7 +616,7 @@ def test_expert_sort_gather_and_combine():
     g = torch.Generator().manual_seed(4)
     n, top, E, width = 150, 3, 7, 24
     ids = torch.stack([torch.randperm(E, generator=g)[:top] for _ in range(n)]).to(torch.int32)
-    counts, order, place = ops.expert_sort(ids.to(DEV), E)
+    counts, order, place, _ = ops.expert_sort(ids.to(DEV), E)
     counts, order, place = counts.cpu(), order.cpu().long(), place.cpu().long()
     assert torch.equal(counts.long(), torch.bincount(ids.view(-1).long(), minlength=E))
     assert torch.equal(order[place], torch.arange(n * top))
@@ -626,6 +630,42 @@ def test_expert_sort_gather_and_combine():
     got = ops.combine_rows(y.to(DEV), place.to(torch.int32).to(DEV), wts.to(DEV)).cpu()
     want = (y[place].view(n, top, width).double() * wts.double()[:, :, None]).sum(1)
     assert (got - want).abs().max() < 1e-5
+    # padded: every expert's stretch starts at a multiple of 16 places, the places in between hold -1 and gather zeros
+    counts2, order2, place2, tile_group = ops.expert_sort(ids.to(DEV), E, pad=16)
+    order2, place2, tile_group = order2.cpu().long(), place2.cpu().long(), tile_group.cpu().long()
+    assert torch.equal(counts2.cpu(), counts.to(torch.int32)) and order2.numel() % 16 == 0 and order2.numel() >= n * top + E * 15
+    assert torch.equal(order2[place2], torch.arange(n * top))
+    starts = torch.cat([torch.zeros(1, dtype=torch.long), ((counts + 15) // 16 * 16).cumsum(0)])
+    for e in range(E):
+        stretch = order2[starts[e]:starts[e + 1]]
+        assert torch.all(ids.view(-1)[stretch[:counts[e]]] == e) and torch.all(stretch[counts[e]:] == -1)
+        assert torch.all(tile_group[starts[e] // 16:starts[e + 1] // 16] == e)
+    assert torch.all(order2[starts[-1]:] == -1)
+    rows2 = ops.gather_rows(x.to(DEV), order2.to(torch.int32).to(DEV), top).cpu()
+    assert torch.equal(rows2[order2 >= 0], x[order2[order2 >= 0] // top]) and torch.all(rows2[order2 < 0] == 0)
+
+
+@pytest.mark.parametrize("n_in,n_out,groups", [(64, 48, 3), (256, 200, 5), (72, 16, 1)])
+def test_grouped_product(n_in, n_out, groups):
+    """Rows ordered by the matrix they multiply, each group padded to whole tiles: one launch against the products group by group."""
+    from oxr_inference_b200 import ops
+
+    g = torch.Generator().manual_seed(n_in)
+    tiles = [2, 0, 1, 3, 1][:groups]
+    group_of_tile = [e for e, c in enumerate(tiles) for _ in range(c)] + [-1]         # a last tile nobody uses: not computed
+    rows = len(group_of_tile) * ops.GROUP_TILE_ROWS
+    x = torch.randn(rows, n_in, generator=g).to(torch.bfloat16)
+    w = (torch.randn(groups * n_out, n_in, generator=g) * 0.2).to(torch.bfloat16)
+    got = ops.grouped_linear(x.to(DEV), w.to(DEV), torch.tensor(group_of_tile, dtype=torch.int32, device=DEV), n_out).float().cpu()
+    squared = ops.grouped_linear(x.to(DEV), w.to(DEV), torch.tensor(group_of_tile, dtype=torch.int32, device=DEV), n_out, relu2=True).float().cpu()
+    for t, e in enumerate(group_of_tile):
+        lo = t * ops.GROUP_TILE_ROWS
+        if e < 0:
+            assert torch.all(got[lo:lo + ops.GROUP_TILE_ROWS] == 0)
+            continue
+        want = x[lo:lo + ops.GROUP_TILE_ROWS].double() @ w[e * n_out:(e + 1) * n_out].double().T
+        assert (got[lo:lo + ops.GROUP_TILE_ROWS] - want).abs().max() <= 2e-2 * want.abs().max(), f"tile {t} of group {e}"
+        assert (squared[lo:lo + ops.GROUP_TILE_ROWS] - torch.relu(want) ** 2).abs().max() <= 2e-2 * (want.abs().max() ** 2), f"tile {t}: relu squared"
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
