@@ -72,15 +72,17 @@ struct __align__(16) Bf16x8 { __nv_bfloat162 v[4]; };
 
 template <bool ROLL>
 __global__ void conv_qkv_store_bf16x8_kernel(
-    __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ v_out, const __nv_bfloat16* __restrict__ proj, int proj_stride, int cq, int ck,
-    int cv, int taps, const float* __restrict__ wt, const float* __restrict__ bias, float* __restrict__ tails, long long slot_stride,
+    __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ v_out, const __nv_bfloat16* __restrict__ proj, int n_tokens, int proj_stride,
+    int cq, int ck, int cv, int taps, const float* __restrict__ wt, const float* __restrict__ bias, float* __restrict__ tails, long long slot_stride,
     const int* __restrict__ req_of_token, const int* __restrict__ cu_q, const int* __restrict__ state_slots, const int* __restrict__ positions,
     float temp_coef, int temp_every, const float* __restrict__ blend, const __nv_bfloat16* __restrict__ first, __nv_bfloat16* __restrict__ k_pool,
     __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ slots, long long n_slots, int* status) {
-    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8;
-    const int t = blockIdx.x;
+    // a block: 8 neighbouring tokens (one per warp) x 256 channels (8 per lane), so that the rows a token shares with its neighbours
+    // come out of this SM's L1
+    const int c = (blockIdx.y * 32 + (threadIdx.x & 31)) * 8;
+    const int t = blockIdx.x * 8 + (threadIdx.x >> 5);
     const int channels = cq + ck + cv;
-    if (c >= channels) return;
+    if (c >= channels || t >= n_tokens) return;
     const int r = ROLL ? t : req_of_token[t];
     const int i = ROLL ? 0 : t - cu_q[r];
     float b[8], acc[8], cur[8], wj[8];
@@ -213,10 +215,10 @@ OXR_API int oxr_conv_qkv_store(void* q_out, void* v_out, const void* proj, int n
     if (dtype == 1 && cq % 8 == 0 && ck % 8 == 0 && cv % 8 == 0 && proj_stride % 8 == 0 && aligned(proj) && aligned(q_out) && aligned(v_out) &&
         aligned(first) && aligned(k_pool) && aligned(v_pool) && (taps == 0 || wt != nullptr) && aligned(wt) && aligned(bias)) {
         using B = __nv_bfloat16;
-        dim3 vgrid(n_tokens, (channels / 8 + threads - 1) / threads);
+        dim3 vgrid((n_tokens + 7) / 8, (channels / 8 + 31) / 32);
         const bool single = n_tokens == n_requests && single_tokens;
 #define OXR_CONV_QKV8(ROLL) \
-        conv_qkv_store_bf16x8_kernel<ROLL><<<vgrid, threads, 0, stream>>>((B*)q_out, (B*)v_out, (const B*)proj, proj_stride, cq, ck, cv, taps, wt, bias, \
+        conv_qkv_store_bf16x8_kernel<ROLL><<<vgrid, 256, 0, stream>>>((B*)q_out, (B*)v_out, (const B*)proj, n_tokens, proj_stride, cq, ck, cv, taps, wt, bias, \
                                                                          tails, slot_stride, req_of_token, cu_q, state_slots, positions, temp_coef, \
                                                                          temp_every, blend, (const B*)first, (B*)k_pool, (B*)v_pool, slots, n_slots, status)
         if (single) {
