@@ -15,13 +15,20 @@
 // Also here: a bias row added to a matrix in place and an fp32 matrix scaled in place.
 #include "common.cuh"
 
+// Per-head widths: q and k heads have dk entries, v heads dv; in memory a q head takes qw entries, a cached key head kw and a cached
+// value head vw (wider than dk / dv when the cache pads keys and values to one size for the tiled attention kernels; the padding
+// is never written and stays zero).
+struct HeadWidths {
+    int dk, dv, qw, kw, vw;
+};
+
 template <typename T>
 __global__ void conv_qkv_store_kernel(
     T* __restrict__ q_out, T* __restrict__ v_out, const T* __restrict__ proj, int proj_stride, int cq, int ck, int cv, int taps,
     const float* __restrict__ w, const float* __restrict__ bias, const float* __restrict__ tails, long long slot_stride,
     const int* __restrict__ req_of_token, const int* __restrict__ cu_q, const int* __restrict__ state_slots,
     const int* __restrict__ positions, float temp_coef, int temp_every, const float* __restrict__ blend, const T* __restrict__ first,
-    T* __restrict__ k_pool, T* __restrict__ v_pool, const int* __restrict__ slots, long long n_slots, int* status) {
+    T* __restrict__ k_pool, T* __restrict__ v_pool, const int* __restrict__ slots, long long n_slots, int* status, const HeadWidths hw) {
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     const int t = blockIdx.x;
     const int channels = cq + ck + cv;
@@ -43,14 +50,15 @@ __global__ void conv_qkv_store_kernel(
     }
     if (c < cq) {
         if (temp_every > 0) acc *= 1.f + temp_coef * logf((float)((positions[t] + 1) / temp_every + 1));
-        q_out[(size_t)t * cq + c] = Num<T>::from_f32(acc);
+        q_out[(size_t)t * (cq / hw.dk) * hw.qw + (c / hw.dk) * hw.qw + c % hw.dk] = Num<T>::from_f32(acc);
         return;
     }
     const long long slot = slots[t];
     if (slot >= n_slots) oxr_report(status, OXR_BAD_SLOT, t);
     const bool store = slot >= 0 && slot < n_slots;
     if (c < cq + ck) {
-        if (store) k_pool[slot * ck + (c - cq)] = Num<T>::from_f32(acc);
+        const int kc = c - cq;
+        if (store) k_pool[slot * (ck / hw.dk) * hw.kw + (kc / hw.dk) * hw.kw + kc % hw.dk] = Num<T>::from_f32(acc);
         return;
     }
     const int cc = c - cq - ck;
@@ -60,7 +68,7 @@ __global__ void conv_qkv_store_kernel(
     }
     const T rounded = Num<T>::from_f32(acc);
     if (v_out != nullptr) v_out[(size_t)t * cv + cc] = rounded;
-    if (store) v_pool[slot * cv + cc] = rounded;
+    if (store) v_pool[slot * (cv / hw.dv) * hw.vw + (cc / hw.dv) * hw.vw + cc % hw.dv] = rounded;
 }
 
 
@@ -76,7 +84,7 @@ __global__ void conv_qkv_store_bf16x8_kernel(
     int cq, int ck, int cv, int taps, const float* __restrict__ wt, const float* __restrict__ bias, float* __restrict__ tails, long long slot_stride,
     const int* __restrict__ req_of_token, const int* __restrict__ cu_q, const int* __restrict__ state_slots, const int* __restrict__ positions,
     float temp_coef, int temp_every, const float* __restrict__ blend, const __nv_bfloat16* __restrict__ first, __nv_bfloat16* __restrict__ k_pool,
-    __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ slots, long long n_slots, int* status) {
+    __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ slots, long long n_slots, int* status, const HeadWidths hw) {
     // a block: 8 neighbouring tokens (one per warp) x 256 channels (8 per lane), so that the rows a token shares with its neighbours
     // come out of this SM's L1
     const int c = (blockIdx.y * 32 + (threadIdx.x & 31)) * 8;
@@ -146,14 +154,15 @@ __global__ void conv_qkv_store_bf16x8_kernel(
 #pragma unroll
             for (int k = 0; k < 8; ++k) acc[k] *= f;
         }
-        *reinterpret_cast<Bf16x8*>(q_out + (size_t)t * cq + c) = pack(acc);
+        *reinterpret_cast<Bf16x8*>(q_out + (size_t)t * (cq / hw.dk) * hw.qw + (c / hw.dk) * hw.qw + c % hw.dk) = pack(acc);
         return;
     }
     const long long slot = slots[t];
     if (slot >= n_slots) oxr_report(status, OXR_BAD_SLOT, t);
     const bool store = slot >= 0 && slot < n_slots;
     if (c < cq + ck) {
-        if (store) *reinterpret_cast<Bf16x8*>(k_pool + slot * ck + (c - cq)) = pack(acc);
+        const int kc = c - cq;
+        if (store) *reinterpret_cast<Bf16x8*>(k_pool + slot * (ck / hw.dk) * hw.kw + (kc / hw.dk) * hw.kw + kc % hw.dk) = pack(acc);
         return;
     }
     const int cc = c - cq - ck;
@@ -169,7 +178,7 @@ __global__ void conv_qkv_store_bf16x8_kernel(
     }
     const Bf16x8 rounded = pack(acc);
     if (v_out != nullptr) *reinterpret_cast<Bf16x8*>(v_out + (size_t)t * cv + cc) = rounded;
-    if (store) *reinterpret_cast<Bf16x8*>(v_pool + slot * cv + cc) = rounded;
+    if (store) *reinterpret_cast<Bf16x8*>(v_pool + slot * (cv / hw.dv) * hw.vw + (cc / hw.dv) * hw.vw + cc % hw.dv) = rounded;
 }
 
 // After the convolution read it: the tail becomes the last taps-1 values of (old tail ++ the step's proj + bias).
@@ -193,9 +202,11 @@ OXR_API int oxr_conv_qkv_store(void* q_out, void* v_out, const void* proj, int n
                                int taps, const float* w, const float* wt, const float* bias, float* tails, long long slot_stride, const int* req_of_token,
                                const int* cu_q, const int* state_slots, const int* positions, float temp_coef, int temp_every,
                                const float* blend, const void* first, void* k_pool, void* v_pool, const int* slots, long long n_slots, int dtype,
-                               int single_tokens, int* status, cudaStream_t stream) {
+                               int single_tokens, int dk, int dv, int qw, int kw, int vw, int* status, cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     const int channels = cq + ck + cv;
+    if (dk <= 0 || dv <= 0 || cq % dk || ck % dk || cv % dv || qw < dk || kw < dk || vw < dv) return OXR_BAD_ARGUMENT;
+    const HeadWidths hw = {dk, dv, qw, kw, vw};
     if (cq <= 0 || ck <= 0 || cv <= 0 || taps < 0 || proj_stride < channels || n_requests <= 0 || (taps > 0 && w == nullptr) ||
         (taps > 1 && tails == nullptr) || (blend != nullptr && first == nullptr))
         return OXR_BAD_ARGUMENT;
@@ -206,13 +217,13 @@ OXR_API int oxr_conv_qkv_store(void* q_out, void* v_out, const void* proj, int n
     do { \
         conv_qkv_store_kernel<T><<<grid, threads, 0, stream>>>((T*)q_out, (T*)v_out, (const T*)proj, proj_stride, cq, ck, cv, taps, w, bias, tails, \
                                                               slot_stride, req_of_token, cu_q, state_slots, positions, temp_coef, temp_every, blend, \
-                                                              (const T*)first, (T*)k_pool, (T*)v_pool, slots, n_slots, status); \
+                                                              (const T*)first, (T*)k_pool, (T*)v_pool, slots, n_slots, status, hw); \
         if (taps > 1) \
             conv_qkv_roll_kernel<T><<<roll, threads, 0, stream>>>(tails, slot_stride, (const T*)proj, proj_stride, channels, taps, bias, cu_q, \
                                                                  state_slots); \
     } while (0)
     const auto aligned = [](const void* p) { return p == nullptr || (reinterpret_cast<uintptr_t>(p) & 15) == 0; };
-    if (dtype == 1 && cq % 8 == 0 && ck % 8 == 0 && cv % 8 == 0 && proj_stride % 8 == 0 && aligned(proj) && aligned(q_out) && aligned(v_out) &&
+    if (dtype == 1 && dk % 8 == 0 && dv % 8 == 0 && qw % 8 == 0 && kw % 8 == 0 && vw % 8 == 0 && proj_stride % 8 == 0 && aligned(proj) && aligned(q_out) && aligned(v_out) &&
         aligned(first) && aligned(k_pool) && aligned(v_pool) && (taps == 0 || wt != nullptr) && aligned(wt) && aligned(bias)) {
         using B = __nv_bfloat16;
         dim3 vgrid((n_tokens + 7) / 8, (channels / 8 + 31) / 32);
@@ -220,7 +231,7 @@ OXR_API int oxr_conv_qkv_store(void* q_out, void* v_out, const void* proj, int n
 #define OXR_CONV_QKV8(ROLL) \
         conv_qkv_store_bf16x8_kernel<ROLL><<<vgrid, 256, 0, stream>>>((B*)q_out, (B*)v_out, (const B*)proj, n_tokens, proj_stride, cq, ck, cv, taps, wt, bias, \
                                                                          tails, slot_stride, req_of_token, cu_q, state_slots, positions, temp_coef, \
-                                                                         temp_every, blend, (const B*)first, (B*)k_pool, (B*)v_pool, slots, n_slots, status)
+                                                                         temp_every, blend, (const B*)first, (B*)k_pool, (B*)v_pool, slots, n_slots, status, hw)
         if (single) {
             OXR_CONV_QKV8(true);
         } else {

@@ -159,7 +159,10 @@ def bifusun_model_spec(c: BifusunConfig) -> ModelSpec:
         final_norm=norm("final.norm"),
         head=PartSpec("linear_head", {"vocab_size": c.vocab, "hidden_size": c.width, "tied": False, "scale": c.logit_scale}, prefix="head",
                       names={"weight": ""}),
-        max_positions=MAX_POSITIONS, eos_token_ids=c.eos_token_ids)
+        max_positions=MAX_POSITIONS, eos_token_ids=c.eos_token_ids,
+        # tensors a checkpoint may carry for layers that do not use them (a blending weight where nothing is blended, the second norm of
+        # a layer without a feed-forward); names that a part claims are never matched against these
+        ignored_tensors=(r"l\d+\.mix\.vmix", r"l\d+\.norm2"))
 
 
 BIFUSUN = register_architecture(Architecture("Bifusun", BifusunConfig.from_dict, bifusun_model_spec))

@@ -138,7 +138,7 @@ def _lib():
         lib.oxr_scatter_rows.argtypes = [p, ll, ll, p, i, i, i, p, i, i, p, p, ll, i, p]
         lib.oxr_latent_prep.argtypes = [p, ll, ll, p, i, i, p, f, p, i, i, i, p, i, i, p, p, i, p, i, i, p, p]
         lib.oxr_head_linear.argtypes = [p, i, i, p, i, i, p, i, i, i, i, i, p]
-        lib.oxr_conv_qkv_store.argtypes = [p, p, p, i, i, i, i, i, i, i, p, p, p, p, ll, p, p, p, p, f, i, p, p, p, p, p, ll, i, i, p, p]
+        lib.oxr_conv_qkv_store.argtypes = [p, p, p, i, i, i, i, i, i, i, p, p, p, p, ll, p, p, p, p, f, i, p, p, p, p, p, ll, i, i, i, i, i, i, i, p, p]
         lib.oxr_add_bias.argtypes = [p, p, i, i, i, p]
         lib.oxr_scale_f32.argtypes = [p, f, ll, p]
         lib.oxr_mlstm_scan.argtypes = [p, p, p, i, i, i, i, i, p, p, i, i, i, f, f, p, ll, p, p, i, p]
@@ -1257,7 +1257,8 @@ def conv_qkv_store(proj: torch.Tensor, cq: int, ck: int, cv: int, *, conv: torch
                    k_pool: torch.Tensor, v_pool: torch.Tensor, slots: torch.Tensor, req_of_token: torch.Tensor, cu_q: torch.Tensor,
                    state_slots: torch.Tensor, positions: torch.Tensor, n_requests: int, status: torch.Tensor, temp_coef: float = 0.0,
                    temp_every: int = 0, blend: torch.Tensor | None = None, first: torch.Tensor | None = None, keep_values: bool = False,
-                   single_tokens: bool = False, conv_t: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor | None]:
+                   single_tokens: bool = False, conv_t: torch.Tensor | None = None, q_head_width: int | None = None
+                   ) -> tuple[torch.Tensor, torch.Tensor | None]:
     """From a packed step's stacked projection ``proj [tokens, >= cq + ck + cv]`` to queries and cache rows in one launch (and one more that
     rolls the tails): add ``bias [cq + ck + cv]``, filter every channel causally with ``conv [channels, taps]`` (the last tap meets the current
     token; what stands before a step's first token comes from the request's ``tails`` row ``[channels, taps - 1]``, zero for a new request,
@@ -1266,7 +1267,9 @@ def conv_qkv_store(proj: torch.Tensor, cq: int, ck: int, cv: int, *, conv: torch
     ``k_pool`` / ``v_pool`` (one layer's ``[pages, page_size, KV, D]``) at ``slots`` (-1 skips). ``conv`` None: no filter. ``conv_t``: the same filter
     transposed, ``[taps, channels]``, which the 16-byte bfloat16 kernel reads (without it the scalar kernel runs). ``single_tokens``: the
     caller knows that every request brings exactly one token (token r is request r's); the bfloat16 kernel then rolls the tails itself.
-    Returns the queries ``[tokens, cq]`` and, with ``keep_values``, the values ``[tokens, cv]`` as they were cached."""
+    The pools' last axis may be wider than a key or value head (a cache that pads both to one size): only the first entries of each head are
+    written. ``q_head_width``: the width a query head takes in the result (zeros behind its entries; default: its own size).
+    Returns the queries ``[tokens, heads * q_head_width]`` and, with ``keep_values``, the values ``[tokens, cv]`` as they were cached."""
     _need(proj, "proj")
     _need(k_pool, "k_pool", proj.dtype)
     _need(v_pool, "v_pool", proj.dtype)
@@ -1288,20 +1291,25 @@ def conv_qkv_store(proj: torch.Tensor, cq: int, ck: int, cv: int, *, conv: torch
     if taps > 1:
         if tails is None or tails.dtype != torch.float32 or tails.stride(-1) != 1 or tails[0].numel() < channels * (taps - 1):
             raise KernelError("conv_qkv_store: the tails must be fp32 rows of channels x (taps - 1) with a dense last axis")
-    if k_pool[0, 0].numel() != ck or v_pool[0, 0].numel() != cv or k_pool.shape[:2] != v_pool.shape[:2]:
+    kv_heads, kw, vw = k_pool.shape[2], k_pool.shape[3], v_pool.shape[3]
+    if ck % kv_heads or cv % kv_heads or k_pool.shape[:3] != v_pool.shape[:3]:
         raise KernelError("conv_qkv_store: the pools do not fit the key and value columns")
+    dk, dv = ck // kv_heads, cv // kv_heads
+    qw = dk if q_head_width is None else int(q_head_width)
+    if kw < dk or vw < dv or qw < dk or cq % dk:
+        raise KernelError("conv_qkv_store: a head of the pools or of the result is narrower than the projection's")
     if blend is not None:
         _need(blend, "blend", torch.float32)
         _need(first, "first", proj.dtype)
         if first.shape != (n, cv):
             raise KernelError("conv_qkv_store: the values to blend with must be [tokens, cv]")
-    q = torch.empty((n, cq), dtype=proj.dtype, device=proj.device)
+    q = (torch.empty if qw == dk else torch.zeros)((n, cq // dk * qw), dtype=proj.dtype, device=proj.device)
     v = torch.empty((n, cv), dtype=proj.dtype, device=proj.device) if keep_values else None
     _done(_lib().oxr_conv_qkv_store(q.data_ptr(), _ptr(v), proj.data_ptr(), n, n_requests, proj.shape[1], cq, ck, cv, taps, _ptr(conv), _ptr(conv_t) if conv is not None else None, _ptr(bias),
                                     _ptr(tails), tails.stride(0) if tails is not None else 0, req_of_token.data_ptr(), cu_q.data_ptr(),
                                     state_slots.data_ptr(), positions.data_ptr(), float(temp_coef), int(temp_every), _ptr(blend), _ptr(first),
                                     k_pool.data_ptr(), v_pool.data_ptr(), slots.data_ptr(), k_pool.shape[0] * k_pool.shape[1], _dtype_code(proj),
-                                    int(bool(single_tokens) and n == n_requests), status.data_ptr(), _stream()), "conv_qkv_store")
+                                    int(bool(single_tokens) and n == n_requests), dk, dv, qw, kw, vw, status.data_ptr(), _stream()), "conv_qkv_store")
     global launch_count
     launch_count += 1 if taps > 1 and not (single_tokens and n == n_requests and proj.dtype == torch.bfloat16 and conv_t is not None) else 0
     return q, v

@@ -84,9 +84,21 @@ class MaskedAttention(Mixer):
         return self.biases or self.taps > 0 or self.temp_every > 0 or self.value_mix is not None
 
     @property
+    def padded(self) -> int:
+        """The one size that keys and values are padded to in the cache (0: no padding). Where keys and values differ in size, the
+        tiled tensor-core kernels would not take them; a bfloat16 mixer that writes its cache through ``conv_qkv_store`` and has a plain
+        mask therefore keeps both at the larger size (the padding stays zero: it adds nothing to a score and its share of the output
+        is dropped), which costs cache space and buys the TMA / tcgen05 kernels instead of the CUDA-core one."""
+        size = max(self.DK, self.DV)
+        if (self.DK != self.DV and self.between and self.chunk == 0 and self.bias_rows == 0 and self.DK % 8 == 0 and self.DV % 8 == 0
+                and ops.tiled_attention_takes(size, size, self.runtime.dtype)):
+            return size
+        return 0
+
+    @property
     def plain(self) -> bool:
         """Causal or windowed softmax over keys and values of one size: what the TMA / tcgen05 attention kernels take."""
-        return self.chunk == 0 and self.bias_rows == 0 and self.DK == self.DV
+        return self.chunk == 0 and self.bias_rows == 0 and (self.DK == self.DV or self.padded > 0)
 
     def _vector_shapes(self) -> dict[str, tuple[int, ...]]:
         out: dict[str, tuple[int, ...]] = {}
@@ -133,7 +145,7 @@ class MaskedAttention(Mixer):
 
     def cache_need(self):
         # keys and values of one size under a causal or windowed mask: the need of plain grouped-query attention, whose pools get TMA maps
-        paged = (PagedKVNeed(self.KV, self.DK, self.window) if self.plain else
+        paged = (PagedKVNeed(self.KV, self.padded or self.DK, self.window) if self.plain else
                  PagedKVNeed(self.KV, self.DK, self.window, value_dim=self.DV, chunk=self.chunk))
         if self.taps > 1:
             return paged, StateNeed(((self.cq + self.ck + self.cv) * (self.taps - 1),), torch.float32)
@@ -141,15 +153,15 @@ class MaskedAttention(Mixer):
 
     @property
     def tiled(self) -> bool:
-        return ops.tiled_attention_takes(self.DK, self.DV, self.runtime.dtype)
+        return self.padded > 0 or ops.tiled_attention_takes(self.DK, self.DV, self.runtime.dtype)
 
     def kernel_head_dims(self) -> tuple[int, ...]:
-        return (self.DK,) if self.tiled else ()
+        return (self.padded or self.DK,) if self.tiled else ()
 
     def tile_specs(self) -> list[tuple[int, int, int]]:
         if not self.tiled:
             return []
-        return ops.attention_tile_specs(self.H, self.KV, self.DK, self.runtime.dtype, self.runtime.page_size if self.plain else None)
+        return ops.attention_tile_specs(self.H, self.KV, self.padded or self.DK, self.runtime.dtype, self.runtime.page_size if self.plain else None)
 
     def forward(self, h: torch.Tensor, ctx: StepContext, cache: LayerCache) -> torch.Tensor:
         y = self.out(self._attend(h, ctx, cache))
@@ -173,16 +185,23 @@ class MaskedAttention(Mixer):
                 qkv, self.cq, self.ck, self.cv, conv=self.qkv_conv, conv_t=self.qkv_conv_t, bias=self.qkv_bias, tails=cache.state, k_pool=k_pool, v_pool=v_pool,
                 slots=group.slots if cache.store else ctx.no_store_slots, req_of_token=ctx.req_of_token, cu_q=ctx.cu_q,
                 state_slots=ctx.state_slots, positions=ctx.positions, n_requests=ctx.n_requests, status=ctx.status, temp_coef=self.temp_coef,
-                temp_every=self.temp_every, blend=blend, first=first, keep_values=self.value_mix == "keep", single_tokens=ctx.single_tokens)
+                temp_every=self.temp_every, blend=blend, first=first, keep_values=self.value_mix == "keep", single_tokens=ctx.single_tokens,
+                q_head_width=self.padded or None)
             if self.value_mix == "keep":
                 ctx.shared[self.value_mix_key] = kept
-            q_width = self.cq
+            q_width = q.shape[1]
         else:
             if cache.store:
                 ops.scatter_rows(k_pool, qkv, self.cq, group.slots, ctx.status, pool2=v_pool)   # the k columns, then the v columns
             q, q_width = qkv, qkv.shape[1]
         if self.tiled and q.dtype == torch.bfloat16:
             # keys and values of one size the tiled kernels are built for: tensor cores, split-KV for single tokens
+            if self.padded:
+                o = ops.paged_attention(q.view(ctx.n_tokens, self.H, self.padded), k_pool, v_pool, tiles=ctx.tiles, cu_q=ctx.cu_q, ctx_lens=ctx.ctx_lens,
+                                        block_table=group.block_table, page_size=group.page_size, scale=self.scale, window=self.window,
+                                        kv_len_bound=ctx.kv_len_bound, status=ctx.status, kv_maps=group.kv_maps, layer_in_pool=cache.layer_in_group,
+                                        uneven=ctx.uneven)
+                return o[:, :, :self.DV].contiguous().view(ctx.n_tokens, self.H * self.DV)   # the padding's share of the output is dropped
             q = (q if q_width == self.cq else q[:, :self.cq].contiguous()).view(ctx.n_tokens, self.H, self.DK)
             if self.plain:
                 o = ops.paged_attention(q, k_pool, v_pool, tiles=ctx.tiles, cu_q=ctx.cu_q, ctx_lens=ctx.ctx_lens, block_table=group.block_table,

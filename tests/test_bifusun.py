@@ -115,3 +115,14 @@ def test_plain_matrix_memory_matches_its_own_decoding():
     whole = BP.forward(cfg, w, ids)
     for n in (1, 5, 12):
         assert torch.allclose(BP.forward(cfg, w, ids[:n])[-1], whole[n - 1], atol=1e-10)
+
+
+def test_unused_tensors_of_a_layer_may_be_present(tmp_path):
+    """A checkpoint that also stores a blending weight for a layer that blends nothing, and the second norm of a layer without a
+    feed-forward, still fits the model; any other stray tensor does not."""
+    import re
+
+    spec = _model(BU.MODEL_P).spec
+    allowed = [re.compile(p + "$") for p in spec.ignored_tensors]
+    assert any(r.match("l3.mix.vmix") for r in allowed) and any(r.match("l12.norm2") for r in allowed)
+    assert not any(r.match(name) for r in allowed for name in ("l3.mix.q.conv", "l3.mix.vmixer", "xl3.norm2", "l3.norm21", "head"))

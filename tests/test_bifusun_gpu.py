@@ -81,6 +81,9 @@ SINGLE = {
     "tiled_sizes_many_heads": BU.model_config([A(dim=16, vdim=16, heads=20, kv_heads=1, scale=0.2)]),
     "tma_sizes_blended": BU.model_config([A(dim=64, vdim=64, heads=4, kv_heads=2, scale=0.125, v_mix=True), A(dim=64, vdim=64, heads=2, kv_heads=2, scale=0.125, v_mix=True)]),
     "tma_sizes_128": BU.model_config([A(dim=128, vdim=128, heads=2, kv_heads=1, scale=0.09)], width=64),
+    "values_narrower_than_keys": BU.model_config([A(dim=64, vdim=32, heads=4, kv_heads=2, scale=0.125, v_mix=True), A(dim=64, vdim=32, heads=2, kv_heads=2, scale=0.125, v_mix=True)]),
+    "values_wider_than_keys": BU.model_config([A(dim=32, vdim=64, heads=4, kv_heads=1, scale=0.2)]),
+    "values_three_times_the_keys": BU.model_config([A(dim=16, vdim=48, heads=2, kv_heads=2, conv=2)]),
     "matrix_memory": BU.model_config([M()]),
     "matrix_memory_wide_keys": BU.model_config([M(heads=1, dim=70, vdim=40, cap=4.0)]),
     "matrix_memory_many_heads": BU.model_config([M(heads=5, dim=8, vdim=8, cap=30.0)], width=40),
@@ -335,6 +338,31 @@ def test_filter_kernel_with_tails_across_steps(dtype, taps, transposed):
             last = (proj[r][:, :C].float() + bias)[-(taps - 1):].T
             assert torch.allclose(tail, last, atol=1e-6), "the tail holds the last projected values, oldest first"
     assert torch.all(tails[:, C * max(taps - 1, 0):] == 0), "nothing was written beyond a slot's tail"
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_filter_kernel_writes_into_heads_wider_than_its_own(dtype):
+    """Pools and queries whose heads are wider than the projection's (keys and values padded to one size): every head's entries land at
+    the head's start and the padding is left alone."""
+    from oxr_inference_b200 import ops
+
+    g = torch.Generator().manual_seed(8)
+    H, KV, DK, DV, P, n = 4, 2, 8, 16, 4, 6
+    cq, ck, cv = H * DK, KV * DK, KV * DV
+    proj = torch.randn(n, cq + ck + cv, generator=g).to(dtype)
+    k_pool = torch.full((3, P, KV, 24), 7.0, dtype=dtype, device=DEV)
+    v_pool = torch.full((3, P, KV, 24), 7.0, dtype=dtype, device=DEV)
+    i32 = lambda x: torch.tensor(x, dtype=torch.int32, device=DEV)  # noqa: E731
+    slots = [5, 6, 7, 8, 0, 1]
+    q, _ = ops.conv_qkv_store(proj.to(DEV), cq, ck, cv, conv=None, bias=None, tails=None, k_pool=k_pool, v_pool=v_pool, slots=i32(slots),
+                              req_of_token=i32([0] * 4 + [1] * 2), cu_q=i32([0, 4, 6]), state_slots=i32([0, 1]), positions=i32([0, 1, 2, 3, 0, 1]),
+                              n_requests=2, status=ops.new_status(DEV), q_head_width=24)
+    q = q.view(n, H, 24).cpu()
+    assert torch.equal(q[:, :, :DK], proj[:, :cq].view(n, H, DK)) and torch.all(q[:, :, DK:] == 0)
+    k_rows, v_rows = k_pool.view(-1, KV, 24)[slots].cpu(), v_pool.view(-1, KV, 24)[slots].cpu()
+    assert torch.equal(k_rows[:, :, :DK], proj[:, cq:cq + ck].view(n, KV, DK)) and torch.all(k_rows[:, :, DK:] == 7)
+    assert torch.equal(v_rows[:, :, :DV], proj[:, cq + ck:].view(n, KV, DV)) and torch.all(v_rows[:, :, DV:] == 7)
+    assert (k_pool == 7).sum() == k_pool.numel() - n * ck
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
