@@ -72,12 +72,58 @@ __global__ void conv_qkv_store_kernel(
 }
 
 
+struct __align__(16) Bf16x8 { __nv_bfloat162 v[4]; };
+
+// What happens to 8 neighbouring filtered channels of token t: queries get their temperature and go to q_out; keys go to their
+// cache slot; values are blended, kept for later layers if asked, and go to their cache slot.
+__device__ __forceinline__ void conv_finish8(float* acc, int c, int t, __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ v_out, int cq,
+                                             int ck, int cv, const int* __restrict__ positions, float temp_coef, int temp_every,
+                                             const float* __restrict__ blend, const __nv_bfloat16* __restrict__ first,
+                                             __nv_bfloat16* __restrict__ k_pool, __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ slots,
+                                             long long n_slots, int* status, const HeadWidths& hw) {
+    auto pack = [&](const float* x) {
+        Bf16x8 out;
+#pragma unroll
+        for (int k = 0; k < 4; ++k) out.v[k] = __floats2bfloat162_rn(x[2 * k], x[2 * k + 1]);
+        return out;
+    };
+    if (c < cq) {
+        if (temp_every > 0) {
+            const float f = 1.f + temp_coef * logf((float)((positions[t] + 1) / temp_every + 1));
+#pragma unroll
+            for (int k = 0; k < 8; ++k) acc[k] *= f;
+        }
+        *reinterpret_cast<Bf16x8*>(q_out + (size_t)t * (cq / hw.dk) * hw.qw + (c / hw.dk) * hw.qw + c % hw.dk) = pack(acc);
+        return;
+    }
+    const long long slot = slots[t];
+    if (slot >= n_slots) oxr_report(status, OXR_BAD_SLOT, t);
+    const bool store = slot >= 0 && slot < n_slots;
+    if (c < cq + ck) {
+        const int kc = c - cq;
+        if (store) *reinterpret_cast<Bf16x8*>(k_pool + slot * (ck / hw.dk) * hw.kw + (kc / hw.dk) * hw.kw + kc % hw.dk) = pack(acc);
+        return;
+    }
+    const int cc = c - cq - ck;
+    if (blend != nullptr) {
+        const float lam = blend[0];
+        const Bf16x8 raw = *reinterpret_cast<const Bf16x8*>(first + (size_t)t * cv + cc);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __bfloat1622float2(raw.v[k]);
+            acc[2 * k] = (1.f - lam) * acc[2 * k] + lam * f.x;
+            acc[2 * k + 1] = (1.f - lam) * acc[2 * k + 1] + lam * f.y;
+        }
+    }
+    const Bf16x8 rounded = pack(acc);
+    if (v_out != nullptr) *reinterpret_cast<Bf16x8*>(v_out + (size_t)t * cv + cc) = rounded;
+    if (store) *reinterpret_cast<Bf16x8*>(v_pool + slot * (cv / hw.dv) * hw.vw + (cc / hw.dv) * hw.vw + cc % hw.dv) = rounded;
+}
+
 // The same for bfloat16 with 16-byte accesses: a thread takes 8 neighbouring channels (all of q, of k or of v: the three widths are
 // multiples of 8). Its filter comes transposed, wt [taps, channels], so that a thread's 8 weights of a tap are 32 contiguous bytes and a
 // warp's are one run (read from [channels, taps], every load of a warp touched 32 lines, and the kernel was slower than the scalar one). ROLL: every request brings exactly one token (a decode step), so the thread that filters a channel is the only one
 // that reads its tail and rolls it forward itself; otherwise the roll kernel follows.
-struct __align__(16) Bf16x8 { __nv_bfloat162 v[4]; };
-
 template <bool ROLL>
 __global__ void conv_qkv_store_bf16x8_kernel(
     __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ v_out, const __nv_bfloat16* __restrict__ proj, int n_tokens, int proj_stride,
@@ -142,43 +188,82 @@ __global__ void conv_qkv_store_bf16x8_kernel(
             }
         }
     }
-    auto pack = [&](const float* x) {
-        Bf16x8 out;
-#pragma unroll
-        for (int k = 0; k < 4; ++k) out.v[k] = __floats2bfloat162_rn(x[2 * k], x[2 * k + 1]);
-        return out;
+    conv_finish8(acc, c, t, q_out, v_out, cq, ck, cv, positions, temp_coef, temp_every, blend, first, k_pool, v_pool, slots, n_slots, status, hw);
+}
+
+// Portions of prompts, filters of 2 to 4 taps: a warp walks over TOK neighbouring tokens and keeps the filter's weights and the last
+// TAPS-1 rows in registers, so every row is read once (and TAPS-1 rows before the warp's first token), the weights once a warp.
+// Whether a row belongs to the token's own request is decided tap by tap (a row of the packed step before the request's first token
+// of this step is another request's: the request's tail stands in for it).
+template <int TAPS, int TOK>
+__global__ void __launch_bounds__(256) conv_qkv_store_bf16x8_window_kernel(
+    __nv_bfloat16* __restrict__ q_out, __nv_bfloat16* __restrict__ v_out, const __nv_bfloat16* __restrict__ proj, int n_tokens, int proj_stride,
+    int cq, int ck, int cv, const float* __restrict__ wt, const float* __restrict__ bias, const float* __restrict__ tails, long long slot_stride,
+    const int* __restrict__ req_of_token, const int* __restrict__ cu_q, const int* __restrict__ state_slots, const int* __restrict__ positions,
+    float temp_coef, int temp_every, const float* __restrict__ blend, const __nv_bfloat16* __restrict__ first, __nv_bfloat16* __restrict__ k_pool,
+    __nv_bfloat16* __restrict__ v_pool, const int* __restrict__ slots, long long n_slots, int* status, const HeadWidths hw) {
+    const int c = (blockIdx.y * 32 + (threadIdx.x & 31)) * 8;
+    const int t0 = (blockIdx.x * 8 + (threadIdx.x >> 5)) * TOK;
+    const int channels = cq + ck + cv;
+    if (c >= channels || t0 >= n_tokens) return;
+    float b[8], w[TAPS][8], win[TAPS - 1][8];
+    auto load8f = [&](const float* src, float* out) {
+        const float4 lo = *reinterpret_cast<const float4*>(src), hi = *reinterpret_cast<const float4*>(src + 4);
+        out[0] = lo.x; out[1] = lo.y; out[2] = lo.z; out[3] = lo.w;
+        out[4] = hi.x; out[5] = hi.y; out[6] = hi.z; out[7] = hi.w;
     };
-    if (c < cq) {
-        if (temp_every > 0) {
-            const float f = 1.f + temp_coef * logf((float)((positions[t] + 1) / temp_every + 1));
+    if (bias != nullptr) load8f(bias + c, b);
+    else
 #pragma unroll
-            for (int k = 0; k < 8; ++k) acc[k] *= f;
-        }
-        *reinterpret_cast<Bf16x8*>(q_out + (size_t)t * (cq / hw.dk) * hw.qw + (c / hw.dk) * hw.qw + c % hw.dk) = pack(acc);
-        return;
-    }
-    const long long slot = slots[t];
-    if (slot >= n_slots) oxr_report(status, OXR_BAD_SLOT, t);
-    const bool store = slot >= 0 && slot < n_slots;
-    if (c < cq + ck) {
-        const int kc = c - cq;
-        if (store) *reinterpret_cast<Bf16x8*>(k_pool + slot * (ck / hw.dk) * hw.kw + (kc / hw.dk) * hw.kw + kc % hw.dk) = pack(acc);
-        return;
-    }
-    const int cc = c - cq - ck;
-    if (blend != nullptr) {
-        const float lam = blend[0];
-        const Bf16x8 raw = *reinterpret_cast<const Bf16x8*>(first + (size_t)t * cv + cc);
+        for (int k = 0; k < 8; ++k) b[k] = 0.f;
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) load8f(wt + (size_t)j * channels + c, w[j]);
+    auto load8 = [&](int row, float* out) {
+        const Bf16x8 raw = *reinterpret_cast<const Bf16x8*>(proj + (size_t)row * proj_stride + c);
 #pragma unroll
         for (int k = 0; k < 4; ++k) {
             const float2 f = __bfloat1622float2(raw.v[k]);
-            acc[2 * k] = (1.f - lam) * acc[2 * k] + lam * f.x;
-            acc[2 * k + 1] = (1.f - lam) * acc[2 * k + 1] + lam * f.y;
+            out[2 * k] = f.x + b[2 * k];
+            out[2 * k + 1] = f.y + b[2 * k + 1];
         }
+    };
+#pragma unroll
+    for (int j = 0; j < TAPS - 1; ++j) {       // win[j]: the row TAPS-1-j tokens before the current one
+        const int row = t0 - (TAPS - 1) + j;
+        if (row >= 0) load8(row, win[j]);
+        else
+#pragma unroll
+            for (int k = 0; k < 8; ++k) win[j][k] = 0.f;
     }
-    const Bf16x8 rounded = pack(acc);
-    if (v_out != nullptr) *reinterpret_cast<Bf16x8*>(v_out + (size_t)t * cv + cc) = rounded;
-    if (store) *reinterpret_cast<Bf16x8*>(v_pool + slot * (cv / hw.dv) * hw.vw + (cc / hw.dv) * hw.vw + cc % hw.dv) = rounded;
+#pragma unroll
+    for (int n = 0; n < TOK; ++n) {
+        const int t = t0 + n;
+        if (t >= n_tokens) break;
+        const int r = req_of_token[t], i = t - cu_q[r];
+        const float* tail = tails + (long long)state_slots[r] * slot_stride + (long long)c * (TAPS - 1);
+        float cur[8], acc[8];
+        load8(t, cur);
+#pragma unroll
+        for (int k = 0; k < 8; ++k) acc[k] = w[TAPS - 1][k] * cur[k];
+#pragma unroll
+        for (int j = 0; j < TAPS - 1; ++j) {
+            const int back = TAPS - 1 - j;
+            if (i - back >= 0) {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] = fmaf(w[j][k], win[j][k], acc[k]);
+            } else {
+#pragma unroll
+                for (int k = 0; k < 8; ++k) acc[k] = fmaf(w[j][k], tail[k * (TAPS - 1) + TAPS - 1 + (i - back)], acc[k]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j + 1 < TAPS - 1; ++j)
+#pragma unroll
+            for (int k = 0; k < 8; ++k) win[j][k] = win[j + 1][k];
+#pragma unroll
+        for (int k = 0; k < 8; ++k) win[TAPS - 2][k] = cur[k];
+        conv_finish8(acc, c, t, q_out, v_out, cq, ck, cv, positions, temp_coef, temp_every, blend, first, k_pool, v_pool, slots, n_slots, status, hw);
+    }
 }
 
 // After the convolution read it: the tail becomes the last taps-1 values of (old tail ++ the step's proj + bias).
@@ -232,13 +317,21 @@ OXR_API int oxr_conv_qkv_store(void* q_out, void* v_out, const void* proj, int n
         conv_qkv_store_bf16x8_kernel<ROLL><<<vgrid, 256, 0, stream>>>((B*)q_out, (B*)v_out, (const B*)proj, n_tokens, proj_stride, cq, ck, cv, taps, wt, bias, \
                                                                          tails, slot_stride, req_of_token, cu_q, state_slots, positions, temp_coef, \
                                                                          temp_every, blend, (const B*)first, (B*)k_pool, (B*)v_pool, slots, n_slots, status, hw)
+#define OXR_CONV_QKV8W(TAPS) \
+        conv_qkv_store_bf16x8_window_kernel<TAPS, 4><<<dim3((n_tokens + 31) / 32, (channels / 8 + 31) / 32), 256, 0, stream>>>( \
+            (B*)q_out, (B*)v_out, (const B*)proj, n_tokens, proj_stride, cq, ck, cv, wt, bias, tails, slot_stride, req_of_token, cu_q, state_slots, \
+            positions, temp_coef, temp_every, blend, (const B*)first, (B*)k_pool, (B*)v_pool, slots, n_slots, status, hw)
         if (single) {
             OXR_CONV_QKV8(true);
         } else {
-            OXR_CONV_QKV8(false);
+            if (taps == 2 && n_tokens >= 64) OXR_CONV_QKV8W(2);
+            else if (taps == 3 && n_tokens >= 64) OXR_CONV_QKV8W(3);
+            else if (taps == 4 && n_tokens >= 64) OXR_CONV_QKV8W(4);
+            else OXR_CONV_QKV8(false);
             if (taps > 1)
                 conv_qkv_roll_kernel<B><<<roll, threads, 0, stream>>>(tails, slot_stride, (const B*)proj, proj_stride, channels, taps, bias, cu_q, state_slots);
         }
+#undef OXR_CONV_QKV8W
 #undef OXR_CONV_QKV8
         return oxr_launch_status();
     }

@@ -1436,8 +1436,8 @@ def grouped_linear(x: torch.Tensor, weight: torch.Tensor, tile_group: torch.Tens
                    relu2: bool = False) -> torch.Tensor:
     """``out[r] = x[r] @ weight[g n : (g + 1) n].T`` with ``g = tile_group[r // GROUP_TILE_ROWS]``: rows ordered by the matrix they multiply (each
     group padded to whole tiles of rows), ``weight [groups * n, k]`` the matrices stacked. One launch of the TMA + tcgen05 kernel, whatever
-    the groups' sizes, which stay on the device. A tile whose group is -1 is not computed (its rows of ``out`` are zero). ``relu2``: the
-    epilogue writes ``relu(out)^2`` of the fp32 sums."""
+    the groups' sizes, which stay on the device. A tile whose group is -1 is not computed (its rows of ``out`` are left unwritten: nobody
+    may read them). ``relu2``: the epilogue writes ``relu(out)^2`` of the fp32 sums."""
     _need(x, "x", torch.bfloat16)
     _need(weight, "weight", torch.bfloat16)
     _need(tile_group, "tile_group", torch.int32)
@@ -1445,7 +1445,7 @@ def grouped_linear(x: torch.Tensor, weight: torch.Tensor, tile_group: torch.Tens
     if weight.shape[1] != k or weight.shape[0] % n or m % GROUP_TILE_ROWS or tile_group.numel() != m // GROUP_TILE_ROWS or k % 8:
         raise KernelError("grouped_linear: sizes do not fit")
     out_dtype = out_dtype or x.dtype
-    out = torch.zeros((m, n), dtype=out_dtype, device=x.device)
+    out = torch.empty((m, n), dtype=out_dtype, device=x.device)
     tile_n, _ = _gemm_plan(m, n, k, False)
     _done(_lib().oxr_gemm_tcgen05_grouped_bf16(out.data_ptr(), x.data_ptr(), weight.data_ptr(), m, n, k, weight.shape[0] // n, tile_group.data_ptr(),
                                                _DT[out_dtype], tile_n, int(relu2), new_status(x.device).data_ptr(), _stream()), "gemm_tcgen05_grouped")
