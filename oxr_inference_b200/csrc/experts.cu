@@ -70,13 +70,88 @@ __global__ void route_kernel(float* __restrict__ gate, int* __restrict__ ids, fl
     }
 }
 
+
+// The same choice with one WARP per token (up to 256 experts and 32 groups): lane l scores the experts l, l + 32, ..., the scores
+// meet in shared memory, lane g adds up group g's two largest, and every pick (of a group, then of an expert) is one warp-wide
+// maximum in which the lower index wins a tie. A decode step's handful of tokens costs a few microseconds instead of a serial walk.
+constexpr int ROUTE_WARP_MAX_E = 256;
+
+__device__ __forceinline__ void warp_argmax(float& v, int& idx) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, v, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+        if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
+    }
+}
+
+__global__ void __launch_bounds__(128) route_warp_kernel(float* __restrict__ gate, int* __restrict__ ids, float* __restrict__ wts, const float* __restrict__ z,
+                                                        int n_tokens, int E, int top, int groups, int keep, float scale) {
+    __shared__ float sc[4][ROUTE_WARP_MAX_E];
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= n_tokens) return;
+    float* s = sc[warp];
+    const int per = E / groups;
+    for (int e = lane; e < E; e += 32) s[e] = 1.f / (1.f + expf(-z[(size_t)t * E + e]));
+    __syncwarp();
+    unsigned allowed = 0xffffffffu;            // one bit per group
+    if (groups > 1 && keep < groups) {
+        float score = -INFINITY;               // lane g: group g
+        if (lane < groups) {
+            float a = -1.f, b = -1.f;
+            for (int e = lane * per; e < (lane + 1) * per; ++e) {
+                const float v = s[e];
+                if (v > a) { b = a; a = v; }
+                else if (v > b) b = v;
+            }
+            score = a + (b >= 0.f ? b : 0.f);
+        }
+        allowed = 0u;
+        for (int i = 0; i < keep; ++i) {
+            float v = ((allowed >> lane) & 1u) ? -INFINITY : score;
+            int idx = lane;
+            warp_argmax(v, idx);
+            allowed |= 1u << (idx & 31);
+        }
+    }
+    float sum = 0.f, mine_s = 0.f;
+    int mine = -1;                             // lane i keeps the i-th pick
+    for (int i = 0; i < top; ++i) {
+        float v = -INFINITY;
+        int idx = 0x7fffffff;
+        for (int e = lane; e < E; e += 32) {
+            const float x = s[e];              // -1 once chosen
+            if (x >= 0.f && ((allowed >> (e / per)) & 1u) && x > v) { v = x; idx = e; }
+        }
+        warp_argmax(v, idx);
+        if (idx >= E) { idx = -1; v = 0.f; }       // nothing left to pick (scores that are not numbers): no expert, no weight
+        if (lane == i) { mine = idx; mine_s = v; }
+        if (lane == 0 && idx >= 0) s[idx] = -1.f;
+        sum += v;
+        __syncwarp();
+    }
+    const float norm = scale / (sum + 1e-20f);
+    for (int e = lane; e < E; e += 32) gate[(size_t)t * E + e] = 0.f;
+    __syncwarp();
+    if (lane < top) {
+        const float w = mine_s * norm;
+        if (mine >= 0) gate[(size_t)t * E + mine] = w;
+        ids[(size_t)t * top + lane] = mine;
+        wts[(size_t)t * top + lane] = w;
+    }
+}
+
 OXR_API int oxr_route(float* gate, int* ids, float* wts, const float* z, int n_tokens, int E, int top, int groups, int keep, float scale,
                       cudaStream_t stream) {
     if (n_tokens <= 0) return 0;
     if (E <= 0 || top <= 0 || top > E || top > ROUTE_MAX_TOP || groups <= 0 || groups > ROUTE_MAX_GROUPS || E % groups || keep <= 0 || keep > groups ||
         top > keep * (E / groups))
         return OXR_BAD_ARGUMENT;
-    route_kernel<<<(n_tokens + 63) / 64, 64, 0, stream>>>(gate, ids, wts, z, n_tokens, E, top, groups, keep, scale);
+    if (E <= ROUTE_WARP_MAX_E && groups <= 32)
+        route_warp_kernel<<<(n_tokens + 3) / 4, 128, 0, stream>>>(gate, ids, wts, z, n_tokens, E, top, groups, keep, scale);
+    else
+        route_kernel<<<(n_tokens + 63) / 64, 64, 0, stream>>>(gate, ids, wts, z, n_tokens, E, top, groups, keep, scale);
     return oxr_launch_status();
 }
 

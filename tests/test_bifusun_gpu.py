@@ -450,7 +450,8 @@ def test_head_norm_with_gate(dtype):
     assert (got - want).abs().max() <= (1e-5 if dtype == torch.float32 else 2e-2) * want.abs().max()
 
 
-@pytest.mark.parametrize("E,top,groups,keep", [(12, 4, 4, 3), (6, 2, 3, 2), (8, 3, 1, 1), (5, 2, 5, 3), (64, 8, 8, 4), (9, 1, 3, 1), (4, 4, 2, 2)])
+@pytest.mark.parametrize("E,top,groups,keep", [(12, 4, 4, 3), (6, 2, 3, 2), (8, 3, 1, 1), (5, 2, 5, 3), (64, 8, 8, 4), (9, 1, 3, 1), (4, 4, 2, 2), (256, 32, 32, 9),
+                                               (320, 6, 64, 20), (66, 3, 33, 4)])
 def test_router_kernel(E, top, groups, keep):
     from oxr_inference_b200 import ops
 
