@@ -439,10 +439,10 @@ def bifusun_config(width: int, ff: int, heads: int, kv_heads: int, head_dim: int
     """A Bifusun model of a real model's layer sizes: a matrix-memory layer, then three attention layers (biases, a filter of four taps, a
     query temperature, blended values), in turn; each with a feed-forward of ``experts`` experts of which a token runs ``top``, whose
     ``top`` experts together are as wide as the dense feed-forward of the Qwen3 model beside it."""
-    moe = {"kind": "moe", "expert": {"ff": ff // top}, "router": {"experts": experts, "top": top, "scale": 2.5, "groups": {"count": 4, "keep": 3}}}
+    moe = {"kind": "moe", "expert": {"ff": ff // top}, "router": {"experts": experts, "top": top, "scale": 2.0, "groups": {"count": 8, "keep": 4}}}
     attention = {"type": "attention", "mlp": moe, "mixer": {
         "heads": heads, "kv_heads": kv_heads, "dim": head_dim, "vdim": head_dim, "scale": head_dim ** -0.5, "conv": 4,
-        "q_temp": {"coef": 0.5, "every": 128}, "v_mix": True}}
+        "q_temp": {"coef": 0.3, "every": 256}, "v_mix": True}}
     mlstm = {"type": "mlstm", "mlp": moe, "mixer": {"heads": 8, "dim": width // 16, "vdim": width // 8, "gate_cap": 15.0}}
     turn = [mlstm, attention, attention, attention]
     return {"architecture": "Bifusun", "embedding": {"scale": 1.0}, "logit_scale": 1.0, "norm": {"eps": 1e-6}, "vocab": vocab, "width": width,
@@ -505,7 +505,7 @@ def bifusun_kernels(width: int, heads: int, kv_heads: int, head_dim: int, ff: in
         state_slots = i32(list(range(len(q_lens))))
         ms = _time_ms(lambda: ops.conv_qkv_store(qkv, cq, ck, cv, conv=conv, conv_t=conv_t, bias=bias, tails=tails, k_pool=k_pool, v_pool=v_pool, slots=slots,
                                                  req_of_token=req, cu_q=cu, state_slots=state_slots, positions=pos, n_requests=len(q_lens),
-                                                 status=status, temp_coef=0.5, temp_every=128, blend=lam, first=first,
+                                                 status=status, temp_coef=0.3, temp_every=256, blend=lam, first=first,
                                                  single_tokens=len(q_lens) > 1), flush=flush)
         put(f"conv_qkv_store {name} (bias, 4 taps, temperature, blend, cache write, tail roll)", f"qk_norm_rope_store {name}", ms,
             bytes_=n * (C * 2 * 2 + cv * 2) + len(q_lens) * C * (taps - 1) * 8)
@@ -548,19 +548,19 @@ def bifusun_kernels(width: int, heads: int, kv_heads: int, head_dim: int, ff: in
     from oxr_inference_b200.parts.experts import RoutedExperts
 
     part = RoutedExperts(Runtime(device=torch.device(dev), dtype=bf, max_positions=1, status=status), hidden_size=width, intermediate_size=ffe,
-                         experts=E, top=top, groups=4, keep=3, scale=2.5)
+                         experts=E, top=top, groups=8, keep=4, scale=2.0)
     part.router, part.up, part.down = router_w, up_w, down_w
     part.finish_loading()
     for n in (T, B):
         h = rand(n, width)
         z = torch.randn(n, E, device=dev)
-        ms = _time_ms(lambda: ops.route(z, top=top, groups=4, keep=3, scale=2.5), flush=flush)
+        ms = _time_ms(lambda: ops.route(z, top=top, groups=8, keep=4, scale=2.0), flush=flush)
         put(f"route {n} rows", None, ms, bytes_=n * (E * 8 + top * 8))
         gu = rand(n, 2 * ff)
         ms = _time_ms(lambda: ops.silu_mul(gu), flush=flush)
         put(f"silu_mul {n} rows", None, ms, bytes_=n * ff * 6)
         u = rand(n, E * ffe)
-        gate = ops.route(z, top=top, groups=4, keep=3, scale=2.5)[0]
+        gate = ops.route(z, top=top, groups=8, keep=4, scale=2.0)[0]
         ms = _time_ms(lambda: ops.gated_relu2(u, gate, ffe), flush=flush)
         put(f"gated_relu2 {n} rows (all {E} experts' columns)", f"silu_mul {n} rows", ms, bytes_=n * E * ffe * 4)
         ms = _time_ms(lambda: ops.linear(ops.silu_mul(ops.linear(h, gate_up_w)), dense_down_w), flush=flush)

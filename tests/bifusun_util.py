@@ -41,8 +41,8 @@ MODEL_P = model_config([attention_layer(v_mix=True, mlp=moe()), mlstm_layer(mlp=
                         attention_layer(v_mix=True, conv=2, every=5, coef=0.9), attention_layer(dim=16, vdim=16, kv_heads=4, conv=4, every=0),
                         attention_layer(v_mix=True, heads=2, kv_heads=2, dim=8, scale=0.5, mlp=moe(count=0, top=1)), mlstm_layer(heads=3, dim=8, vdim=16)])
 MODEL_Q = model_config([mlstm_layer(heads=3, dim=40, vdim=24, cap=5.0, mlp=moe(ff=40, experts=4, top=4, count=2, keep=2, scale=1.0)),
-                        attention_layer(heads=4, kv_heads=1, dim=64, vdim=64, conv=4, every=16, v_mix=True, scale=0.125,
-                                        mlp=moe(ff=8, experts=12, top=4, count=12, keep=5, scale=2.5)),
+                        attention_layer(heads=4, kv_heads=1, dim=64, vdim=64, conv=4, every=16, v_mix=True, scale=0.11,
+                                        mlp=moe(ff=8, experts=10, top=3, count=10, keep=5, scale=2.2)),
                         attention_layer(heads=2, kv_heads=1, dim=64, vdim=64, conv=1, every=3, coef=0.25, v_mix=True, scale=0.2)],
                        width=64, vocab=200, eps=1e-6, scale=0.9, logit_scale=2.0)
 MODEL_R = model_config([attention_layer(heads=6, kv_heads=3, dim=32, vdim=32, conv=0, every=1, coef=0.15, mlp=moe(ff=32, experts=9, top=2, count=3, keep=1)),
