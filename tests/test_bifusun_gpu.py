@@ -248,6 +248,30 @@ def test_greedy_generation_through_the_engine(which, graphs, tmp_path):
         assert engine.counters["graph_steps"] > 0
 
 
+def test_command_line_generates_with_the_design(tmp_path):
+    import json
+    import subprocess
+    import sys
+
+    import util
+
+    cfg = BU.MODEL_R
+    folder = BU.make_folder(tmp_path, cfg, "R", seed=14)
+    plain_cfg, w = BP.read_model(folder, torch.float64)
+    cmd = [sys.executable, "-m", "oxr_inference_b200", "--model", str(folder), "--prompt-ids", "5,17,3", "--prompt-ids", "9 8 7 6 11 2",
+           "--max-tokens", "6", "--dtype", "float32", "--num-pages", "32", "--max-running", "4", "--ignore-eos"]
+    res = subprocess.run(cmd, capture_output=True, text=True, cwd=str(util.ROOT), timeout=600)
+    assert res.returncode == 0, res.stderr
+    rows = [json.loads(line) for line in res.stdout.strip().splitlines() if line.startswith("{")]
+    for row, prompt in zip(rows, ([5, 17, 3], [9, 8, 7, 6, 11, 2])):
+        want, gaps = BP.greedy(plain_cfg, w, prompt, 6)
+        for a, b, gap in zip(row["token_ids"], want, gaps):
+            if gap < 1e-3:
+                break
+            assert a == b, f"the command line generated {row['token_ids']}, the plain implementation {want}"
+    assert len(rows) == 2
+
+
 def test_bfloat16_generation_with_graphs_equals_eager(tmp_path):
     from oxr_inference_b200.config import EngineSettings
     from oxr_inference_b200.engine.api import Engine, SamplingParams
