@@ -235,6 +235,10 @@ __global__ void __launch_bounds__(256) conv_qkv_store_bf16x8_window_kernel(
 #pragma unroll
             for (int k = 0; k < 8; ++k) win[j][k] = 0.f;
     }
+    Bf16x8 rows[TOK];      // the warp's own rows, all requested before the first is used
+#pragma unroll
+    for (int n = 0; n < TOK; ++n)
+        if (t0 + n < n_tokens) rows[n] = *reinterpret_cast<const Bf16x8*>(proj + (size_t)(t0 + n) * proj_stride + c);
 #pragma unroll
     for (int n = 0; n < TOK; ++n) {
         const int t = t0 + n;
@@ -242,7 +246,12 @@ __global__ void __launch_bounds__(256) conv_qkv_store_bf16x8_window_kernel(
         const int r = req_of_token[t], i = t - cu_q[r];
         const float* tail = tails + (long long)state_slots[r] * slot_stride + (long long)c * (TAPS - 1);
         float cur[8], acc[8];
-        load8(t, cur);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+            const float2 f = __bfloat1622float2(rows[n].v[k]);
+            cur[2 * k] = f.x + b[2 * k];
+            cur[2 * k + 1] = f.y + b[2 * k + 1];
+        }
 #pragma unroll
         for (int k = 0; k < 8; ++k) acc[k] = w[TAPS - 1][k] * cur[k];
 #pragma unroll
@@ -318,7 +327,7 @@ OXR_API int oxr_conv_qkv_store(void* q_out, void* v_out, const void* proj, int n
                                                                          tails, slot_stride, req_of_token, cu_q, state_slots, positions, temp_coef, \
                                                                          temp_every, blend, (const B*)first, (B*)k_pool, (B*)v_pool, slots, n_slots, status, hw)
 #define OXR_CONV_QKV8W(TAPS) \
-        conv_qkv_store_bf16x8_window_kernel<TAPS, 4><<<dim3((n_tokens + 31) / 32, (channels / 8 + 31) / 32), 256, 0, stream>>>( \
+        conv_qkv_store_bf16x8_window_kernel<TAPS, 8><<<dim3((n_tokens + 63) / 64, (channels / 8 + 31) / 32), 256, 0, stream>>>( \
             (B*)q_out, (B*)v_out, (const B*)proj, n_tokens, proj_stride, cq, ck, cv, wt, bias, tails, slot_stride, req_of_token, cu_q, state_slots, \
             positions, temp_coef, temp_every, blend, (const B*)first, (B*)k_pool, (B*)v_pool, slots, n_slots, status, hw)
         if (single) {
